@@ -81,14 +81,19 @@ class KVGroup:
         v_shape = shape[:-1] + (request.v_head_dim or request.head_dim,)
         # zeros: a masked key's weight of zero must never meet a NaN left in fresh memory
         self.k = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
-        self.v = torch.zeros(v_shape, dtype=dtype, device=device) if allocate else None
+        if request.keys_only:
+            self.v = self.k                              # one row per position, read as key and as value
+        else:
+            self.v = torch.zeros(v_shape, dtype=dtype, device=device) if allocate else None
         self.index = {c: i for i, c in enumerate(self.cache_ids)}
 
     def pages_for(self, length: int) -> int:
         return (length + self.page_size - 1) // self.page_size
 
     def bytes(self) -> int:
-        return 0 if self.k is None else (self.k.numel() + self.v.numel()) * self.k.element_size()
+        if self.k is None:
+            return 0
+        return (self.k.numel() + (0 if self.request.keys_only else self.v.numel())) * self.k.element_size()
 
 
 class StateGroup:

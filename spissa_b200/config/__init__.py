@@ -5,8 +5,9 @@ from .registry import (UnknownArchitecture, config_class_for, config_from_dict, 
 from .llama import ConfigError, LlamaConfig, RopeScaling
 from .duzinex import DuzinexConfig
 from .gozatar import GozatarConfig
+from .kugirax import KugiraxConfig
 
 __all__ = ["LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule",
            "UnknownArchitecture", "config_class_for", "config_from_dict", "known_architectures",
            "load_config", "register_architecture", "unregister_architecture",
-           "ConfigError", "LlamaConfig", "RopeScaling", "DuzinexConfig", "GozatarConfig"]
+           "ConfigError", "LlamaConfig", "RopeScaling", "DuzinexConfig", "GozatarConfig", "KugiraxConfig"]

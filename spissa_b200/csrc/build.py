@@ -56,6 +56,7 @@ MODULES = {
     "seqmix": "seqmix_kernels.cu",
     "diff_flash": "diff_flash.cu",
     "hybrid": "hybrid_kernels.cu",
+    "latent": "latent_kernels.cu",
 }
 
 

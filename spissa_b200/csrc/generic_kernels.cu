@@ -570,7 +570,8 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
 // visible position; lane j scores key j, the softmax runs online in 32-bit, and lane d
 // owns output dims d, d+32, ... . A token at position p sees keys lo..p with
 // lo = max(0, p-window+1) when window > 0, else 0. All keys, this step's included,
-// are read from the cache.
+// are read from the cache. ``sink`` (float32 per query head, or null): a score that joins the
+// softmax's denominator once and has no value row.
 
 // q · k over hd dims for one key row; 16-byte loads where the row allows them
 __device__ __forceinline__ float ag_dot(const float* __restrict__ qv, const float* __restrict__ kr, int hd) {
@@ -611,7 +612,7 @@ template <typename TQ, typename TC, bool SPLIT>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
                          TQ* __restrict__ out, KvPlace pl, int T, int nh, int nkv, int hd, int vd, int window,
-                         float scale) {
+                         float scale, const float* __restrict__ sink) {
     __shared__ __align__(16) float qs[AG_WARPS][AG_MAX_HD];
     __shared__ float part_ml[AG_WARPS][2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -703,6 +704,16 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
             }
         }
         l = ll;
+        m = mm;
+    }
+    if (sink) {
+        // a sink: one more term e^{sink_h} in the denominator, with no key and no value
+        const float sk = sink[h];
+        const float m_all = fmaxf(m, sk);
+        const float f = expf(m - m_all);
+        l = l * f + expf(sk - m_all);
+#pragma unroll
+        for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] *= f;
     }
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) {
@@ -714,7 +725,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, const void* vpool, int cache_dt,
                                 void* out, const int* token_seq, const int* positions, const int* seq_slot,
                                 const int* page_table, int max_pages, int page_size, int T, int nh, int nkv,
-                                int hd, int vd, int window, float scale, cudaStream_t stream) {
+                                int hd, int vd, int window, float scale, const float* sink, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > AG_MAX_HD) SP_FAIL("attention: head_dim %d is beyond this kernel's limit %d", hd, AG_MAX_HD);
     if (vd <= 0 || vd > AG_MAX_HD) SP_FAIL("attention: value size %d is beyond this kernel's limit %d", vd, AG_MAX_HD);
@@ -728,9 +739,9 @@ SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, cons
 #define AG_LAUNCH(TQ, TC)                                                                                              \
     do {                                                                                                               \
         if (split)                                                                                                     \
-            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale); \
+            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink); \
         else                                                                                                           \
-            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale); \
+            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink); \
     } while (0)
     if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) AG_LAUNCH(float, float);
     else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) AG_LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -764,6 +775,44 @@ SP_API int sp_silu_mul(const void* gu, void* out, int dt, int rows, int I, cudaS
     else if (dt == SP_DT_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, I);
     else SP_FAIL("silu_mul: unsupported dtype code %d", dt);
     SP_CHECK_LAUNCH("silu_mul");
+    return 0;
+}
+
+// ============================================================== cap of the logits, a gate per row
+// x ← cap · tanh(x / cap)
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    const float inv = 1.0f / cap;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x)
+        x[e] = cap * tanhf(x[e] * inv);
+}
+
+SP_API int sp_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.0f)) SP_FAIL("softcap: the cap must be positive");
+    const long long want = (n + 255) / 256;
+    softcap_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(x, (size_t)n, cap);
+    SP_CHECK_LAUNCH("softcap");
+    return 0;
+}
+
+// x[r, :] ← x[r, :] · sigmoid(z[r])
+template <typename T>
+__global__ void scale_rows_sigmoid_kernel(T* __restrict__ x, const float* __restrict__ z, size_t rows, int C) {
+    const size_t n = rows * (size_t)C;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const float g = 1.0f / (1.0f + expf(-z[e / C]));
+        sp_st(x, e, sp_ld(x, e) * g);
+    }
+}
+
+SP_API int sp_scale_rows_sigmoid(void* x, int dt, const float* z, int rows, int C, cudaStream_t stream) {
+    if (rows <= 0 || C <= 0) return 0;
+    const size_t n = (size_t)rows * C;
+    const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    if (dt == SP_DT_F32) scale_rows_sigmoid_kernel<float><<<blocks, 256, 0, stream>>>((float*)x, z, rows, C);
+    else if (dt == SP_DT_BF16) scale_rows_sigmoid_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)x, z, rows, C);
+    else SP_FAIL("scale_rows_sigmoid: unsupported dtype code %d", dt);
+    SP_CHECK_LAUNCH("scale_rows_sigmoid");
     return 0;
 }
 

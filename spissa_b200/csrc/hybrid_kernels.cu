@@ -196,7 +196,8 @@ SP_API int sp_streams_expand(const float* h, float* x, int T, int S, int W, cuda
 }
 
 // ============================================================== short convolution, rotation, unit rms, cache write
-// qkv row (32-bit) = [q: nh·d | k: nkv·d | v: nkv·vd] = C channels. The convolution of channel c at a token reads the
+// qkv row (32-bit) = [q: nh·d | k: nkv·d | v: nkv·vd] = C channels (``v_from_k``: no v channels; the values are the
+// keys as they leave the convolution, before their rotation). The convolution of channel c at a token reads the
 // channel's projected values of the token and of the taps−1 tokens before it: from this step's rows where the step
 // has them, from state[slot][r][c] (r = 0 the oldest) where they came with earlier steps, zeros before the sequence's
 // start (a fresh slot's state is zero). One block per token, a warp per head; the head's values pass through shared
@@ -217,6 +218,7 @@ struct CqArgs {
     float eps, v_scale;
     int unit_rms;                                  // 1: q and k leave with unit rms per head
     int save_inline;                               // 1: every sequence brings one token, so the token's block also shifts the state
+    int v_from_k;                                  // 1: no v channels: the values are the convolved keys, before their rotation
     SpRange rg;
 };
 
@@ -266,7 +268,7 @@ __global__ void __launch_bounds__(CQ_WARPS * 32) conv_qk_store_kernel(CqArgs a) 
     }
     __syncthreads();
     const int d = a.d, vd = a.vd, nh = a.nh, nkv = a.nkv;
-    const int C = (nh + nkv) * d + nkv * vd;
+    const int C = (nh + nkv) * d + (a.v_from_k ? 0 : nkv * vd);
     bool place = true;
     int page = 0;
     {
@@ -278,7 +280,7 @@ __global__ void __launch_bounds__(CQ_WARPS * 32) conv_qk_store_kernel(CqArgs a) 
         }
     }
     const int off = pos % a.page_size;
-    for (int hh = warp; hh < nh + 2 * nkv; hh += CQ_WARPS) {
+    for (int hh = warp; hh < nh + (a.v_from_k ? 1 : 2) * nkv; hh += CQ_WARPS) {
         const bool is_v = hh >= nh + nkv;
         const int size = is_v ? vd : d;
         const int cb = is_v ? (nh + nkv) * d + (hh - nh - nkv) * vd : hh * d;
@@ -291,6 +293,11 @@ __global__ void __launch_bounds__(CQ_WARPS * 32) conv_qk_store_kernel(CqArgs a) 
                 for (int i = lane; i < vd; i += 32) sp_st_dt(a.vpool, a.cache_dt, vb + i, hv[warp][i] * a.v_scale);
             }
             continue;
+        }
+        if (a.v_from_k && hh >= nh && place) {
+            const size_t vb = (((size_t)page * nkv + (hh - nh)) * a.page_size + off) * d;
+            for (int i = lane; i < d; i += 32) sp_st_dt(a.vpool, a.cache_dt, vb + i, hv[warp][i] * a.v_scale);
+            __syncwarp();
         }
         for (int i = lane; i < half; i += 32) {
             const float x0 = hv[warp][i], x1 = hv[warp][i + half];
@@ -345,7 +352,7 @@ __global__ void __launch_bounds__(CQV_WARPS * 32) conv_qk_store_vec_kernel(CqArg
     }
     __syncthreads();
     const int d = a.d, vd = a.vd, nh = a.nh, nkv = a.nkv, n = a.taps - 1;
-    const int C = (nh + nkv) * d + nkv * vd;
+    const int C = (nh + nkv) * d + (a.v_from_k ? 0 : nkv * vd);
     bool place = true;
     int page = 0;
     {
@@ -358,7 +365,7 @@ __global__ void __launch_bounds__(CQV_WARPS * 32) conv_qk_store_vec_kernel(CqArg
     }
     const int off = pos % a.page_size;
     float* st = a.taps > 1 ? a.state + (size_t)slot * n * C : nullptr;
-    for (int hh = warp; hh < nh + 2 * nkv; hh += CQV_WARPS) {
+    for (int hh = warp; hh < nh + (a.v_from_k ? 1 : 2) * nkv; hh += CQV_WARPS) {
         const bool is_v = hh >= nh + nkv;
         const int size = is_v ? vd : d;
         const int cb = is_v ? (nh + nkv) * d + (hh - nh - nkv) * vd : hh * d;
@@ -391,6 +398,14 @@ __global__ void __launch_bounds__(CQV_WARPS * 32) conv_qk_store_vec_kernel(CqArg
                 }
             }
             continue;
+        }
+        if (a.v_from_k && hh >= nh && place) {
+            const size_t vb = (((size_t)page * nkv + (hh - nh)) * a.page_size + off) * d;
+            for (int i = lane * 4; i < d; i += 128) {
+                const float4 v = *(const float4*)&hv[warp][i];
+                cq_store4(a.vpool, a.cache_dt, vb + i, make_float4(v.x * a.v_scale, v.y * a.v_scale, v.z * a.v_scale, v.w * a.v_scale));
+            }
+            __syncwarp();
         }
         for (int i = lane * 4; i < half; i += 128) {
             const float4 x0 = *(const float4*)&hv[warp][i], x1 = *(const float4*)&hv[warp][i + half];
@@ -441,22 +456,23 @@ SP_API int sp_conv_qk_store(const float* qkv, int ld, const void* conv, int conv
                             const int* token_seq, const int* positions, const int* seq_row, const int* page_table,
                             int max_pages, int page_size, const int* seq_start, const int* seq_slot, int T, int B, int nh,
                             int nkv, int d, int vd, float eps, float v_scale, int unit_rms, int all_single,
-                            cudaStream_t stream) {
+                            int v_from_k, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || d > CQ_MAX_DIM || vd <= 0 || vd > CQ_MAX_DIM) SP_FAIL("conv_qk_store: head sizes %d / %d are beyond %d", d, vd, CQ_MAX_DIM);
     if (taps < 1 || taps > CQ_MAX_TAPS) SP_FAIL("conv_qk_store: %d taps, this kernel takes 1 to %d", taps, CQ_MAX_TAPS);
     if (taps > 1 && (!conv || !state)) SP_FAIL("conv_qk_store: a convolution needs its weights and a state");
     if (rd < 0 || (rd & 1) || rd > d) SP_FAIL("conv_qk_store: %d rotated dims do not fit a head of %d", rd, d);
+    if (v_from_k && vd != d) SP_FAIL("conv_qk_store: values that are the keys have the keys' size %d, not %d", d, vd);
     CqArgs a{qkv, ld, conv, conv_dt, taps, state, n_slots, inv_freq, rd, q_out, q_dt, kpool, vpool, cache_dt,
              token_seq, positions, seq_row, page_table, max_pages, page_size, seq_start, seq_slot, T, nh, nkv, d, vd,
-             eps, v_scale, unit_rms, (all_single && taps > 1) ? 1 : 0, sp_range_host};
+             eps, v_scale, unit_rms, (all_single && taps > 1) ? 1 : 0, v_from_k ? 1 : 0, sp_range_host};
     const bool wide = d % 4 == 0 && vd % 4 == 0 && (rd / 2) % 4 == 0 && ld % 4 == 0 &&
                       ((((uintptr_t)qkv) | ((uintptr_t)state) | ((uintptr_t)q_out) | ((uintptr_t)kpool) | ((uintptr_t)vpool)) & 15) == 0;
     if (wide) conv_qk_store_vec_kernel<<<T, CQV_WARPS * 32, 0, stream>>>(a);
     else conv_qk_store_kernel<<<T, CQ_WARPS * 32, 0, stream>>>(a);
     SP_CHECK_LAUNCH("conv_qk_store");
     if (taps > 1 && !all_single) {
-        const int C = (nh + nkv) * d + nkv * vd;
+        const int C = (nh + nkv) * d + (v_from_k ? 0 : nkv * vd);
         conv_state_save_kernel<<<dim3(B, (C + 127) / 128), 128, 0, stream>>>(a, B, C);
         SP_CHECK_LAUNCH("conv_state_save");
     }
@@ -1004,8 +1020,9 @@ SP_API int sp_gelu_tanh(const void* z, int z_dt, void* out, int out_dt, long lon
     return 0;
 }
 
-// g = min(gate, limit), u = clamp(up, ±limit), out = g · sigmoid(slope · g) · (u + 1)
+// g = min(gate, limit), u = clamp(up, ±limit), out = g · sigmoid(slope · g) · (u + 1); slope 0 asks for silu(gate) · up
 __device__ __forceinline__ float hy_clamped_glu(float g, float u, float limit, float slope) {
+    if (slope == 0.0f) return g * hy_sigmoid(g) * u;      // the plain gated unit silu(g) · u: no clamp, no shift
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g * hy_sigmoid(slope * g) * (u + 1.0f);
@@ -1033,7 +1050,8 @@ SP_API int sp_clamped_glu(const void* gu, int gu_dt, void* out, int out_dt, int 
 }
 
 // ============================================================== the router's choice
-// z [T][E] (32-bit logits). s = sigmoid(z); choice c = s + correction. The experts form ``n_groups`` equal groups of
+// z [T][ldz] (32-bit logits, the first E of a row the experts'). s = sigmoid(z), or with ``softmax`` the softmax of
+// the row's E logits; choice c = s + correction (none: s). The weights leave times ``weight_scale``. The experts form ``n_groups`` equal groups of
 // neighbours; a group's score is the sum of its two largest c; only experts of the ``keep`` best groups can be chosen
 // (n_groups ≤ 1: all). The ``top`` largest allowed c are chosen (among equals the lowest index); their weights are
 // their s divided by the sum of those s (+ 1e-20). One warp per token; lane l holds experts l, l+32, ...
@@ -1045,18 +1063,30 @@ __device__ __forceinline__ void ms_take(float& bv, int& bi, float ov, int oi) {
 
 __global__ void __launch_bounds__(MS_WARPS * 32)
 moe_select_kernel(const float* __restrict__ z, const void* __restrict__ corr, int corr_dt, int* __restrict__ ids,
-                  float* __restrict__ wts, int T, int E, int top, int n_groups, int keep) {
+                  float* __restrict__ wts, int T, int E, int ldz, int top, int n_groups, int keep, int softmax,
+                  float weight_scale, float* __restrict__ extra) {
     __shared__ float ch[MS_WARPS][MS_MAX_E];        // choice scores; −inf once chosen or not allowed
     __shared__ float sc[MS_WARPS][MS_MAX_E];
     __shared__ float gs[MS_WARPS][MS_MAX_E];        // group scores
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * MS_WARPS + warp;
     if (t >= T) return;
+    float zmax = -INFINITY, zsum = 1.0f;
+    if (softmax) {
+        // scores: the softmax of the logits over all experts (sums in lane order, then across lanes)
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[(size_t)t * ldz + e]);
+        zmax = sp_warp_max(zmax);
+        float part = 0.0f;
+        for (int e = lane; e < E; e += 32) part += expf(z[(size_t)t * ldz + e] - zmax);
+        zsum = sp_warp_sum(part);
+    }
     for (int e = lane; e < E; e += 32) {
-        const float s = hy_sigmoid(z[(size_t)t * E + e]);
+        const float s = softmax ? expf(z[(size_t)t * ldz + e] - zmax) / zsum : hy_sigmoid(z[(size_t)t * ldz + e]);
         sc[warp][e] = s;
         ch[warp][e] = s + (corr ? sp_ld_dt(corr, corr_dt, e) : 0.0f);
     }
+    // columns beyond the experts' (ldz > E) pass through: a gate's logit that shared the router's product
+    if (extra) for (int e = E + lane; e < ldz; e += 32) extra[(size_t)t * (ldz - E) + (e - E)] = z[(size_t)t * ldz + e];
     __syncwarp();
     if (n_groups > 1) {
         const int gsz = E / n_groups;
@@ -1114,19 +1144,21 @@ moe_select_kernel(const float* __restrict__ z, const void* __restrict__ corr, in
     }
     __syncwarp();
     const float den = sum + 1e-20f;
-    for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] = wts[(size_t)t * top + k] / den;
+    for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] = wts[(size_t)t * top + k] / den * weight_scale;
 }
 
-SP_API int sp_moe_select(const float* z, const void* corr, int corr_dt, int* ids, float* wts, int T, int E, int top,
-                         int n_groups, int keep, cudaStream_t stream) {
+SP_API int sp_moe_select(const float* z, const void* corr, int corr_dt, int* ids, float* wts, int T, int E, int ldz,
+                         int top, int n_groups, int keep, int softmax, float weight_scale, float* extra,
+                         cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || E > MS_MAX_E) SP_FAIL("moe_select: %d experts, this kernel takes up to %d", E, MS_MAX_E);
+    if (ldz < E) SP_FAIL("moe_select: rows of %d logits cannot hold %d experts", ldz, E);
     if (n_groups < 1) n_groups = 1;
     if (E % n_groups) SP_FAIL("moe_select: %d experts do not form %d equal groups", E, n_groups);
     if (n_groups > 1 && (keep < 1 || keep > n_groups)) SP_FAIL("moe_select: %d of %d groups cannot be kept", keep, n_groups);
     const int allowed = n_groups > 1 ? keep * (E / n_groups) : E;
     if (top < 1 || top > allowed) SP_FAIL("moe_select: %d experts cannot be chosen among %d allowed", top, allowed);
-    moe_select_kernel<<<(T + MS_WARPS - 1) / MS_WARPS, MS_WARPS * 32, 0, stream>>>(z, corr, corr_dt, ids, wts, T, E, top, n_groups, keep);
+    moe_select_kernel<<<(T + MS_WARPS - 1) / MS_WARPS, MS_WARPS * 32, 0, stream>>>(z, corr, corr_dt, ids, wts, T, E, ldz, top, n_groups, keep, softmax, weight_scale, extra);
     SP_CHECK_LAUNCH("moe_select");
     return 0;
 }

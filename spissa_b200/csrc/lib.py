@@ -176,10 +176,13 @@ def rope_kv_write(qkv, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd, rd, w
         c_void_p(_ptr(inv_freq)), T, nh, nkv, hd, rd, int(bool(write_kv)), c_void_p(_stream())))
 
 
-def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale, vd=None):
+def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale, vd=None, sink=None):
     """Causal attention of every token of the step over its sequence's cached keys; ``vd``: the size of a value row
-    when it differs from a key row's (``out`` is then [T, nh·vd])."""
+    when it differs from a key row's (``out`` is then [T, nh·vd]). ``sink`` (float32 [nh]): per head a score that joins
+    the softmax's denominator once and has no value."""
     lib = load("generic")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nh):
+        raise KernelError("attention: the sinks are one float32 per query head")
     T = q.shape[0]
     _need_contig(q, out)
     pt = meta.page_table
@@ -188,7 +191,26 @@ def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale, 
         c_void_p(_ptr(q)), dt_code(q), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool),
         c_void_p(_ptr(out)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)),
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
-        T, nh, nkv, hd, int(vd or hd), int(window or 0), c_float(scale), c_void_p(_stream())))
+        T, nh, nkv, hd, int(vd or hd), int(window or 0), c_float(scale), c_void_p(_ptr(sink)), c_void_p(_stream())))
+
+
+def softcap(x, cap: float):
+    """x ← cap · tanh(x / cap), element by element, in place (float32)."""
+    lib = load("generic")
+    if x.dtype != torch.float32:
+        raise KernelError("softcap works on float32 values")
+    _need_contig(x)
+    _check("generic", lib.sp_softcap(c_void_p(_ptr(x)), c_longlong(x.numel()), c_float(cap), c_void_p(_stream())))
+
+
+def scale_rows_sigmoid(x, z):
+    """x[r, :] ← x[r, :] · sigmoid(z[r]) in place; ``z`` float32 [rows] (a gate with one number per token)."""
+    lib = load("generic")
+    if z.dtype != torch.float32 or z.numel() != x.shape[0]:
+        raise KernelError("scale_rows_sigmoid takes one float32 gate per row")
+    _need_contig(x, z)
+    _check("generic", lib.sp_scale_rows_sigmoid(c_void_p(_ptr(x)), dt_code(x), c_void_p(_ptr(z)), x.shape[0], x.shape[1],
+                                                c_void_p(_stream())))
 
 
 def silu_mul(gu, out):
@@ -527,6 +549,11 @@ def flash_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
         return False
     return bool(load("attention").sp_flash_supported(int(hd), int(nh), int(nkv), int(page_size)))
+
+
+def flash_takes_sink() -> bool:
+    """Whether the tensor-core attention kernels take a sink (a score in the denominator that has no key)."""
+    return False
 
 
 def flash_query_tile() -> int:
@@ -1031,11 +1058,12 @@ def streams_expand(h, x, S):
 
 
 def conv_qk_store(qkv, conv, taps, state, q_out, k_pool, v_pool, meta, step, inv_freq, nh, nkv, d, vd, rd, eps,
-                  v_scale=1.0, unit_rms=True):
+                  v_scale=1.0, unit_rms=True, v_from_k=False):
     """``qkv`` rows [q | k | v] (float32): a causal convolution of ``taps`` taps over time on every channel (``conv``
     [C, taps]; ``state`` float32 [slots, taps−1, C] holds each sequence's last inputs), rotation of dim i with dim
     i + rd/2 over the first ``rd`` dims of each q and k head, unit rms per head, q to ``q_out``, k and v (times
-    ``v_scale``) into the paged cache."""
+    ``v_scale``) into the paged cache. ``v_from_k``: rows are [q | k] only and a token's values are its keys as they
+    leave the convolution, before their rotation."""
     lib = load("hybrid")
     if qkv.dtype != torch.float32 or (state is not None and state.dtype != torch.float32):
         raise KernelError("conv_qk_store reads 32-bit projections and keeps a 32-bit state")
@@ -1053,7 +1081,7 @@ def conv_qk_store(qkv, conv, taps, state, q_out, k_pool, v_pool, meta, step, inv
         c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)),
         pt.shape[1], meta.page_size, c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), T, step.n_seqs,
         nh, nkv, d, vd, c_float(eps), c_float(v_scale), int(bool(unit_rms)), int(bool(step.all_single)),
-        c_void_p(_stream())))
+        int(bool(v_from_k)), c_void_p(_stream())))
 
 
 def gla(proj, state, a2, a2_bias, norm_weight, out, step, H, d, vd, rank, tau, eps, out_scale=1.0):
@@ -1109,18 +1137,25 @@ def clamped_glu(gu, out, limit, slope=1.702):
                                         c_float(limit), c_float(slope), c_void_p(_stream())))
 
 
-def moe_select(z, correction, ids, weights, top, n_groups=1, keep=1):
-    """From router logits ``z`` (float32 [T, E]): the ``top`` experts per token by sigmoid(z) + correction among the
-    ``keep`` best of ``n_groups`` groups (a group's score: its two largest), and their weights sigmoid(z) / Σ."""
+def moe_select(z, correction, ids, weights, top, n_groups=1, keep=1, softmax=False, weight_scale=1.0, experts=None,
+               extra=None):
+    """From router logits ``z`` (float32 [T, E]): the ``top`` experts per token by s + correction (s = sigmoid(z), or
+    with ``softmax`` the softmax over the row's experts) among the ``keep`` best of ``n_groups`` groups (a group's
+    score: its two largest), and their weights s / Σ s · ``weight_scale``. ``experts`` < z's columns: the row's other
+    columns are copied to ``extra`` (float32 [T, columns − experts])."""
     lib = load("hybrid")
     if z.dtype != torch.float32 or ids.dtype != torch.int32 or weights.dtype != torch.float32:
         raise KernelError("moe_select takes float32 logits and writes int32 ids and float32 weights")
     _need_contig(z, correction, ids, weights)
-    T, E = z.shape
+    T, ldz = z.shape
+    E = int(experts or ldz)
+    if (extra is None) != (E == ldz) or (extra is not None and (extra.dtype != torch.float32 or extra.numel() != T * (ldz - E))):
+        raise KernelError("moe_select: the columns beyond the experts' need a float32 place to go, and only they")
+    _need_contig(extra)
     _check("hybrid", lib.sp_moe_select(
         c_void_p(_ptr(z)), c_void_p(_ptr(correction)), dt_code(correction) if correction is not None else 0,
-        c_void_p(_ptr(ids)), c_void_p(_ptr(weights)), T, E, int(top), int(n_groups or 1), int(keep or 1),
-        c_void_p(_stream())))
+        c_void_p(_ptr(ids)), c_void_p(_ptr(weights)), T, E, ldz, int(top), int(n_groups or 1), int(keep or 1),
+        int(bool(softmax)), c_float(weight_scale), c_void_p(_ptr(extra)), c_void_p(_stream())))
 
 
 def moe_tile_rows() -> int:
@@ -1185,3 +1220,34 @@ def moe_experts(x, ids, weights, w_gate_up, w_down, y, top, limit, slope=1.702, 
         _w_dt(w_gate_up, w_down), E, c_void_p(_ptr(counts)), c_void_p(_ptr(order)), c_void_p(_ptr(tiles)), max_tiles,
         c_void_p(_ptr(weights)), c_void_p(_ptr(act)), c_void_p(_ptr(out_pairs)), c_void_p(_ptr(y)), T, int(top), W, F,
         c_float(limit), c_float(slope), int(glu_block), c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ latent: attention through a cached low-rank latent
+def latent_norm_store(proj, q_rank, rank, wq, wc, eps, cq_out, pool, meta):
+    """``proj`` rows (float32) = [q part: ``q_rank`` | latent part: ``rank``]: each part's RMS norm with its weight; the
+    q part to ``cq_out`` [T, q_rank], the latent into its page row of ``pool`` ([pages, 1, page_size, rank]; None: the
+    rows carry no latent part)."""
+    lib = load("latent")
+    if proj.dtype != torch.float32:
+        raise KernelError("latent_norm_store reads 32-bit projections")
+    _need_contig(proj, wq, wc, cq_out)
+    pt = meta.page_table
+    if pool is not None:
+        _declare_bounds("latent", lib, _pool_pages(meta, pool), _table_rows(meta, pt), proj.device)
+    _check("latent", lib.sp_latent_norm_store(
+        c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(wq)), c_void_p(_ptr(wc)), _w_dt(*[w for w in (wq, wc) if w is not None]),
+        c_void_p(_ptr(cq_out)), dt_code(cq_out), c_void_p(_ptr(pool)), dt_code(pool) if pool is not None else 0,
+        c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)),
+        pt.shape[1], meta.page_size, proj.shape[0], int(q_rank), int(rank), c_float(eps), c_void_p(_stream())))
+
+
+def headwise_product(a, w, out, H, K_, N, w_rows_are_k):
+    """out[t, h, :] = a[t, h, :] · W_h with ``a`` [T, H·K], ``out`` [T, H·N] and ``w`` the heads' matrices one after
+    another: [H·K, N] (``w_rows_are_k``) or [H·N, K]."""
+    lib = load("latent")
+    _need_contig(a, w, out)
+    if a.shape[1] != H * K_ or out.shape[1] != H * N or w.numel() != H * K_ * N:
+        raise KernelError("headwise_product: the operands' sizes do not fit together")
+    _check("latent", lib.sp_headwise_product(c_void_p(_ptr(a)), dt_code(a), c_void_p(_ptr(w)), dt_code(w), c_void_p(_ptr(out)),
+                                             dt_code(out), a.shape[0], int(H), int(K_), int(N), int(bool(w_rows_are_k)),
+                                             c_void_p(_stream())))

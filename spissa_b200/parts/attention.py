@@ -59,6 +59,7 @@ class GQAAttention(Mixer):
         n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight")
         n.update(names or {})
         self.names = {k: prefix + v for k, v in n.items()}
+        self.sink = None                         # float32 [heads]: per head a score in the softmax's denominator (subclasses)
         self.position = build_part("position", position) if position is not None else None
         if getattr(self.position, "pairing", "half") != "half":
             raise ValueError(f"{prefix}: this mixer's kernels rotate dim i with dim i + rotary_dim/2 only")
@@ -141,7 +142,9 @@ class GQAAttention(Mixer):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         T = q.shape[0]
         ctx = torch.empty_like(q)
-        if K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
+        if self.sink is not None and not K.flash_takes_sink():
+            K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale, sink=self.sink)
+        elif K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
             if step.all_single:
                 # the split is made for the length's bucket, not the length: a step run directly and the same step
                 # replayed from a graph (captured for the bucket) then add up in the same order, bit for bit
@@ -162,5 +165,5 @@ class GQAAttention(Mixer):
                 K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
                                 tiles, nh, nkv, hd, self.window, self.scale)
         else:
-            K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale)
+            K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale, sink=self.sink)
         return ctx

@@ -45,12 +45,15 @@ class KVCacheRequest:
     ``head_dim`` is the size of a key row per kv head, ``v_head_dim`` that of a value row when it differs.
     ``keep_first``: with a window, the first ``keep_first`` positions stay visible to every later query, so the pages
     that hold them are never handed back while the sequence lives.
+    ``keys_only``: a position has ONE row, which its readers take as key and as value (a cached latent): no value pool
+    is allocated and the view's ``v_pool`` is its ``k_pool``.
     """
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     keep_first: int = 0
+    keys_only: bool = False
 
 
 @dataclass(frozen=True)

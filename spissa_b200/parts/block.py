@@ -49,6 +49,32 @@ class PreNormBlock(Block):
         self.ffn.forward(x, step, h)
 
 
+@register_part("block", "parallel_residual")
+class ParallelResidualBlock(Block):
+    """One norm, two readers: with a = norm(h), h += mixer(a) + ffn(a) (not in the reference). Both sublayers add into
+    the 32-bit stream; the feed-forward may be absent. ``norms`` has the one place ``"input"``."""
+    graph_safe = True
+
+    def __init__(self, mixer, ffn, norms: dict, prefix: str = ""):
+        super().__init__(prefix)
+        self.mixer = build_part("mixer", mixer)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.input_norm = build_part("norm", norms["input"])
+
+    def children(self):
+        return [p for p in (self.input_norm, self.mixer, self.ffn) if p is not None]
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, h, step, cache):
+        with phase("input_norm_ms"):
+            x = self.input_norm.forward(h)
+        self.mixer.forward(x, step, cache, h)
+        if self.ffn is not None:
+            self.ffn.forward(x, step, h)
+
+
 @register_part("block", "prenorm_shift")
 class ShiftedPreNormBlock(Block):
     """The pre-norm arrangement with a token shift in front of the mixer:

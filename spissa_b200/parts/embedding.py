@@ -56,9 +56,10 @@ class LMHead(Part):
     graph_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None = None, prefix: str = "",
-                 weight_name: str = "weight"):
+                 weight_name: str = "weight", softcap: float | None = None):
         super().__init__(prefix)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.softcap = float(softcap) if softcap else None       # logits ← cap · tanh(logits / cap)
         self.tied_to = tied_to
         self.weight_name = prefix + weight_name
         self.proj = None
@@ -71,11 +72,16 @@ class LMHead(Part):
         self.proj = Linear(tensors[self.tied_to or self.weight_name])
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.proj(x, out_dtype=torch.float32)
+        logits = self.proj(x, out_dtype=torch.float32)
+        if self.softcap:
+            K.softcap(logits, self.softcap)
+        return logits
 
     def fused_fields(self):
         """What a runner that computes the head itself needs: the weight [vocab, hidden] (bfloat16, contiguous)."""
         w = self.proj.weight if self.proj is not None else None
+        if self.softcap:
+            return None                     # the runners' heads write uncapped logits (a greedy choice needs no cap: ``greedy``)
         if w is None or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.data_ptr() % 16:
             return None
         return dict(kind="linear_head", weight=w, vocab_size=self.vocab_size, hidden_size=self.hidden_size)
@@ -84,7 +90,7 @@ class LMHead(Part):
         """The index of the largest logit of every row (int32 [rows]) without the logits, as the reference's greedy
         head keeps only (best index, best value) while it streams the rows
         (crates/spissa-runtime/src/streaming/linear_argmax.rs:13, streaming/argmax.rs:30-51): the lowest index wins
-        among equal logits. None when no kernel takes these operands (the caller then asks for the logits).
+        among equal logits (a cap of the logits is increasing, so it changes no choice and is left out). None when no kernel takes these operands (the caller then asks for the logits).
         ``note``: the tokens also go into the per-slot headers (an engine's ``step_note()``)."""
         w = self.proj.weight
         if not K.head_argmax_supported(x, w):

@@ -1,0 +1,111 @@
+"""Attention through a cached low-rank latent, as a mixer (not in the reference).
+
+    c_q = n(D_q x) ⊙ w_q                 a low-rank image of the token for the queries,  q_h = U_q,h c_q      [dim]
+    c   = n(D_kv x) ⊙ w_c                the latent [rank]: the ONLY thing cached, one page row per token
+    k_j,h = U_k,h c_j   v_j,h = U_v,h c_j                keys [dim] and values [vdim] of every head are images of c
+    score_h(i, j) = (q_i,h · k_j,h) · scale              over the visible j (``window`` w: i − w < j <= i; None: all j <= i)
+    p_h(i, j) = e^{score} / (e^{sink_h} + Σ_j e^{score})   a learned per-head sink joins the denominator (``sink`` False: none)
+    y += W_o · concat_h(Σ_j p_h(i, j) v_j,h)
+
+n is the RMS norm x / sqrt(mean(x²) + eps). No positions enter. Keys and values are never expanded: since
+q · (U_k c) = (U_kᵀ q) · c and Σ p (U_v c) = U_v (Σ p c), the query is carried into the latent's space once per token,
+the attention runs over the cached rows themselves (one row is key and value, for all heads), and the weighted sum of
+latents is expanded once per token. A layer built with ``shares_latent`` has no D_kv and no norm weight of its own:
+it reads the rows another layer cached (a run with ``cache.writes`` False), with its own U_k, U_v, queries, window
+and sinks. ``cache_window``: the window the cache keeps rows for when readers with other windows share it (None with
+``window`` set: this layer's own).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import lib as K
+from .base import KVCacheRequest, Mixer, WeightSpec
+from .linear import Linear
+from .registry import register_part
+from ..phases import phase
+
+_UNSET = object()
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+    kernel_modules = ("latent",)
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, v_head_dim: int, q_rank: int, kv_rank: int,
+                 scale: float, eps: float, window=None, cache_window=_UNSET, sink: bool = True, shares_latent: bool = False,
+                 prefix: str = "", names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
+        self.q_rank, self.kv_rank = int(q_rank), int(kv_rank)
+        self.scale, self.eps = float(scale), float(eps)
+        self.window = int(window) if window else None
+        self.cache_window = self.window if cache_window is _UNSET else (int(cache_window) if cache_window else None)
+        if self.cache_window is not None and (self.window is None or self.window > self.cache_window):
+            raise ValueError(f"{prefix}: a window of {self.window} sees rows that a cache of {self.cache_window} has returned")
+        self.has_sink, self.shares_latent = bool(sink), bool(shares_latent)
+        n = dict(dq="dq", dq_norm="dq.norm", uq="uq", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", sink="sink", o="o")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.down = self.uq = self.o = self.uk = self.uv = self.sink = self.wq_norm = self.wc_norm = None
+
+    def weight_specs(self):
+        W, H, d, vd, qr, r = self.hidden_size, self.num_heads, self.head_dim, self.v_head_dim, self.q_rank, self.kv_rank
+        n = self.names
+        specs = [WeightSpec(n["dq"], (qr, W)), WeightSpec(n["dq_norm"], (qr,), init="ones"), WeightSpec(n["uq"], (H * d, qr)),
+                 WeightSpec(n["uk"], (H * d, r)), WeightSpec(n["uv"], (H * vd, r)), WeightSpec(n["o"], (W, H * vd))]
+        if not self.shares_latent:
+            specs += [WeightSpec(n["dkv"], (r, W)), WeightSpec(n["dkv_norm"], (r,), init="ones")]
+        if self.has_sink:
+            specs.append(WeightSpec(n["sink"], (H,)))
+        return specs
+
+    def cache_request(self):
+        return KVCacheRequest(1, self.kv_rank, self.cache_window, keys_only=True)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        n = self.names
+        dq = tensors[n["dq"]]
+        self.down_q = Linear(dq)
+        self.down = None if self.shares_latent else Linear(torch.cat([dq, tensors[n["dkv"]]], dim=0))
+        self.wq_norm = tensors[n["dq_norm"]].contiguous()
+        self.wc_norm = None if self.shares_latent else tensors[n["dkv_norm"]].contiguous()
+        self.uq = Linear(tensors[n["uq"]])
+        self.uk = tensors[n["uk"]].contiguous()            # [H·dim, rank]: head h's rows are U_k,h, a matrix [dim, rank]
+        self.uv = tensors[n["uv"]].contiguous()            # [H·vdim, rank]
+        self.o = Linear(tensors[n["o"]])
+        self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None     # a score: 32-bit
+
+    def forward(self, x, step, cache, residual):
+        H, d, vd, qr, r = self.num_heads, self.head_dim, self.v_head_dim, self.q_rank, self.kv_rank
+        T, dev, act = x.shape[0], x.device, self.rt.act_dtype
+        writes = cache.writes
+        if writes and self.shares_latent:
+            raise ValueError(f"{self.prefix}: a layer without a latent projection cannot be the writer of a cache")
+        with phase("latent_projection_ms"):
+            proj = (self.down if writes else self.down_q)(x, out_dtype=torch.float32)     # the norms read unrounded products
+        with phase("latent_norm+append_ms"):
+            cq = torch.empty(T, qr, dtype=act, device=dev)
+            K.latent_norm_store(proj, qr, r, self.wq_norm, self.wc_norm if writes else None, self.eps, cq,
+                                cache.k_pool if writes else None, cache)
+        with phase("q_projection_ms"):
+            q = self.uq(cq)
+            qc = torch.empty(T, H * r, dtype=act, device=dev)
+            K.headwise_product(q, self.uk, qc, H, d, r, w_rows_are_k=True)                # U_k,hᵀ q_h
+        with phase("attention_ms"):
+            mix = self.attend(qc, step, cache)
+        with phase("value_expansion_ms"):
+            ctx = torch.empty(T, H * vd, dtype=act, device=dev)
+            K.headwise_product(mix, self.uv, ctx, H, r, vd, w_rows_are_k=False)           # U_v,h (Σ p c)
+        with phase("o_projection+attention_residual_ms"):
+            self.o(ctx, out=residual, accumulate=True)
+
+    def attend(self, qc, step, cache):
+        """Σ_j p_h(i, j) c_j for queries already in the latent's space: [T, heads·rank]."""
+        H, r = self.num_heads, self.kv_rank
+        mix = torch.empty_like(qc)
+        K.attention_generic(qc, cache.k_pool, cache.k_pool, mix, cache, H, 1, r, self.window, self.scale, sink=self.sink)
+        return mix

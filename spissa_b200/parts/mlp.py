@@ -12,7 +12,13 @@ the reference).
 Clamped GLU feed-forward: g = min(x·Wgᵀ, limit), u = clamp(x·Wuᵀ, ±limit), down( g · sigmoid(slope · g) · (u + 1) ) (not
 in the reference).
 
-Routed experts: ``experts`` clamped-GLU feed-forwards of which each token uses ``top``. s = sigmoid(x·Wrᵀ) in 32-bit;
+A SwiGLU may carry a gate of one number per token: the rows of silu(·) ⊙ (·) are multiplied by ``row_gate`` =
+sigmoid(x · w_sgᵀ) before the down projection (which is linear, so its output is scaled by the same number).
+
+Routed experts: ``experts`` gated feed-forwards (``activation``: ``clamped_glu`` or ``swiglu``) of which each token uses
+``top``. The scores s are ``score`` of the router's 32-bit logits: ``sigmoid``, or ``softmax`` over all experts; the
+weights are s_k / (Σ s_k + 1e-20) · ``weight_scale``. A shared expert may be gated per token by sigmoid(x · w_sgᵀ)
+(``shared_gate`` names the row w_sg; it rides in the router's product). With the sigmoid score: s = sigmoid(x·Wrᵀ) in 32-bit;
 the choice reads s + correction, the weights read s: the experts form ``groups`` equal groups of neighbours, a group's
 score is the sum of its two largest choice scores, only experts of the ``keep_groups`` best groups can be chosen, the
 ``top`` largest choice scores among them are; weight_k = s_k / (Σ s_k + 1e-20); y += Σ_k weight_k · expert_k(x), plus a
@@ -65,9 +71,14 @@ class SwiGLU(FeedForward):
         return dict(kind="swiglu", gate_up=gu.weight, pair=gu.block, down=self.down.weight,
                     hidden_size=self.hidden_size, intermediate_size=self.intermediate_size)
 
-    def forward(self, x, step, residual):
+    takes_row_gate = True
+
+    def forward(self, x, step, residual, row_gate=None):
+        """``row_gate`` (float32 [T]): the token's output is multiplied by sigmoid(row_gate[t])."""
         with phase("gate_projection+up_projection+activation_multiply_ms"):
             act = self.gate_up(x, self.rt.act_dtype)
+            if row_gate is not None:
+                K.scale_rows_sigmoid(act, row_gate)
         with phase("down_projection+mlp_residual_ms"):
             self.down(act, out=residual, accumulate=True)
 
@@ -181,14 +192,21 @@ class RoutedExperts(FeedForward):
     kernel_modules = ("hybrid",)
     kernel_modules_bf16 = ("tc_gemm",)
 
-    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: float,
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: float = 0.0,
                  slope: float = 1.702, groups: int = 1, keep_groups: int = 1, shared=None, prefix: str = "",
-                 names: dict | None = None):
+                 names: dict | None = None, activation: str = "clamped_glu", score: str = "sigmoid",
+                 weight_scale: float = 1.0, correction: bool = True, shared_gate: str | None = None):
         super().__init__(prefix)
+        if activation not in ("clamped_glu", "swiglu") or score not in ("sigmoid", "softmax"):
+            raise ValueError(f"{prefix}: unknown activation {activation!r} or score {score!r}")
+        self.activation, self.score, self.weight_scale = activation, score, float(weight_scale)
+        self.has_correction = bool(correction)
+        self.shared_gate = shared_gate           # name (behind the prefix) of a row [1, hidden]: the shared expert's gate
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.experts, self.top = int(experts), int(top)
         self.groups, self.keep_groups = max(1, int(groups or 1)), int(keep_groups or 1)
-        self.limit, self.slope = float(limit), float(slope)
+        # the kernels read slope 0 as "the plain gated unit silu(g) · u"
+        self.limit, self.slope = (float(limit), float(slope)) if activation == "clamped_glu" else (0.0, 0.0)
         if self.experts % self.groups:
             raise ValueError(f"{prefix}: {self.experts} experts do not form {self.groups} equal groups")
         allowed = self.experts if self.groups == 1 else self.keep_groups * (self.experts // self.groups)
@@ -198,6 +216,8 @@ class RoutedExperts(FeedForward):
         n.update(names or {})
         self.names = n
         self.shared = build_part("ffn", shared) if shared is not None else None
+        if shared_gate and (self.shared is None or not getattr(self.shared, "takes_row_gate", False)):
+            raise ValueError(f"{prefix}: a gate per token needs a shared expert that takes one")
         self.router = self.correction = self.w_gate_up = self.w_down = None
 
     def _expert(self, i: int, which: str) -> str:
@@ -208,8 +228,11 @@ class RoutedExperts(FeedForward):
 
     def weight_specs(self):
         H, I = self.hidden_size, self.intermediate_size
-        specs = [WeightSpec(self.prefix + self.names["router"], (self.experts, H)),
-                 WeightSpec(self.prefix + self.names["correction"], (self.experts,))]
+        specs = [WeightSpec(self.prefix + self.names["router"], (self.experts, H))]
+        if self.has_correction:
+            specs.append(WeightSpec(self.prefix + self.names["correction"], (self.experts,)))
+        if self.shared_gate:
+            specs.append(WeightSpec(self.prefix + self.shared_gate, (1, H)))
         for i in range(self.experts):
             specs += [WeightSpec(self._expert(i, "gate"), (I, H)), WeightSpec(self._expert(i, "up"), (I, H)),
                       WeightSpec(self._expert(i, "down"), (H, I))]
@@ -217,8 +240,11 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.router = Linear(tensors[self.prefix + self.names["router"]])
-        self.correction = tensors[self.prefix + self.names["correction"]].contiguous()
+        router = tensors[self.prefix + self.names["router"]]
+        if self.shared_gate:
+            router = torch.cat([router, tensors[self.prefix + self.shared_gate].reshape(1, -1)], dim=0)
+        self.router = Linear(router)
+        self.correction = tensors[self.prefix + self.names["correction"]].contiguous() if self.has_correction else None
         # [E, 2I, H] and [E, H, I]. An expert's gate rows, then its up rows; for bfloat16 sizes that the tensor-core
         # kernels take, in blocks (``glu_block`` gate rows, then the up rows of the same outputs), so that one tile of a
         # product holds both halves and applies the activation in its epilogue
@@ -244,8 +270,12 @@ class RoutedExperts(FeedForward):
             z = self.router(x, out_dtype=torch.float32)
             ids = torch.empty(T, self.top, dtype=torch.int32, device=x.device)
             wts = torch.empty(T, self.top, dtype=torch.float32, device=x.device)
-            K.moe_select(z, self.correction, ids, wts, self.top, self.groups, self.keep_groups)
+            gate = torch.empty(T, dtype=torch.float32, device=x.device) if self.shared_gate else None
+            K.moe_select(z, self.correction, ids, wts, self.top, self.groups, self.keep_groups,
+                         softmax=self.score == "softmax", weight_scale=self.weight_scale, experts=self.experts, extra=gate)
         with phase("experts_ms"):
             K.moe_experts(x, ids, wts, self.w_gate_up, self.w_down, residual, self.top, self.limit, self.slope, self.glu_block)
-        if self.shared is not None:
+        if self.shared is not None and self.shared_gate:
+            self.shared.forward(x, step, residual, row_gate=gate)
+        elif self.shared is not None:
             self.shared.forward(x, step, residual)
