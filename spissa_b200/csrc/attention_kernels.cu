@@ -113,6 +113,16 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
+    if (kv.sink) {
+        const float sk = kv.sink[h] * LOG2E;           // the row's maximum m is in log2 units
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float m_all = fmaxf(m[r], sk), f = exp2f(m[r] - m_all);
+            l[r] = l[r] * f + exp2f(sk - m_all);
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) { o[i][2 * r] *= f; o[i][2 * r + 1] *= f; }
+        }
+    }
     const int t = lane & 3;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -131,7 +141,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
 template <int HD>
 __device__ __forceinline__ void combine_if_last(const float* part_o, const float* part_ml, int* counters, void* out,
                                                 int out_dt, int b, int g, int G, int nh, int nkv, int n_chunks,
-                                                int* is_last) {
+                                                int* is_last, const float* sink = nullptr) {
     __threadfence();                                    // this CTA's partials are visible before it is counted
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -147,8 +157,10 @@ __device__ __forceinline__ void combine_if_last(const float* part_o, const float
         const size_t bh = (size_t)b * nh + (size_t)g * G + row;
         float mm = -INFINITY;
         for (int c = 0; c < n_chunks; ++c) mm = fmaxf(mm, __ldcg(&part_ml[(bh * n_chunks + c) * 2]));
+        const float sk = sink ? sink[(size_t)g * G + row] * LOG2E : -INFINITY;
+        mm = fmaxf(mm, sk);
         const float msafe = (mm == -INFINITY) ? 0.0f : mm;
-        float ll = 0.0f, acc = 0.0f;
+        float ll = sink ? exp2f(sk - msafe) : 0.0f, acc = 0.0f;
         for (int c = 0; c < n_chunks; ++c) {
             const float lc = __ldcg(&part_ml[(bh * n_chunks + c) * 2 + 1]);
             if (lc > 0.0f) {
@@ -191,7 +203,7 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
             part_ml[(part_base + (size_t)i * n_chunks) * 2] = -INFINITY;
             part_ml[(part_base + (size_t)i * n_chunks) * 2 + 1] = 0.0f;
         }
-        if (counters) combine_if_last<HD>(part_o, part_ml, counters, out, out_dt, b, g, G, nh, kv.nkv, n_chunks, &is_last);
+        if (counters) combine_if_last<HD>(part_o, part_ml, counters, out, out_dt, b, g, G, nh, kv.nkv, n_chunks, &is_last, kv.sink);
         return;
     }
     const int* pt = kv.page_table + (size_t)sp_checked_row(kv.seq_row[b], kv.rg) * kv.max_pages;
@@ -299,18 +311,20 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
         part_o[pi * HD + d] = acc;
         if (d == 0) { part_ml[pi * 2] = mm; part_ml[pi * 2 + 1] = ll; }
     }
-    if (counters) combine_if_last<HD>(part_o, part_ml, counters, out, out_dt, b, g, G, nh, kv.nkv, n_chunks, &is_last);
+    if (counters) combine_if_last<HD>(part_o, part_ml, counters, out, out_dt, b, g, G, nh, kv.nkv, n_chunks, &is_last, kv.sink);
 }
 
 // out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order
 template <typename TO>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                      TO* __restrict__ out, int n_chunks, int HD) {
+                                      TO* __restrict__ out, int n_chunks, int HD, const float* __restrict__ sink, int nh) {
     const size_t bh = blockIdx.x;
     float mm = -INFINITY;
     for (int c = 0; c < n_chunks; ++c) mm = fmaxf(mm, part_ml[(bh * n_chunks + c) * 2]);
+    const float sk = sink ? sink[bh % nh] * LOG2E : -INFINITY;
+    mm = fmaxf(mm, sk);
     const float msafe = (mm == -INFINITY) ? 0.0f : mm;
-    float ll = 0.0f;
+    float ll = sink ? exp2f(sk - msafe) : 0.0f;
     for (int c = 0; c < n_chunks; ++c)
         ll += part_ml[(bh * n_chunks + c) * 2 + 1] * exp2f(part_ml[(bh * n_chunks + c) * 2] - msafe);
     const float inv = 1.0f / ll;
@@ -371,13 +385,14 @@ int launch_flash_prefill_as(dim3 grid, cudaStream_t stream, const __nv_bfloat16*
 }
 }  // namespace
 
-SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
-                            const int* positions, const int* seq_row, const int* page_table, int max_pages,
-                            int page_size, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
-                            float scale, cudaStream_t stream) {
+// ``sink`` (float32 per query head, or null): a score that joins every row's denominator once, with no key and no value
+SP_API int sp_flash_prefill_sink(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
+                                 const int* positions, const int* seq_row, const int* page_table, int max_pages,
+                                 int page_size, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
+                                 float scale, const float* sink, cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
     if (check_common(hd, nh, nkv, page_size)) return 1;
-    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host};
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host, sink};
     if (n_q_tiles > 65535) SP_FAIL("flash_prefill: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
     const float sl = scale * LOG2E;
@@ -392,6 +407,14 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
     }
     SP_CHECK_LAUNCH("flash_prefill");
     return 0;
+}
+
+SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
+                            const int* positions, const int* seq_row, const int* page_table, int max_pages,
+                            int page_size, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
+                            float scale, cudaStream_t stream) {
+    return sp_flash_prefill_sink(q, out, kpool, vpool, seq_start, positions, seq_row, page_table, max_pages, page_size,
+                                 n_seqs, n_q_tiles, nh, nkv, hd, window, scale, nullptr, stream);
 }
 
 namespace {
@@ -430,11 +453,11 @@ SP_API long long sp_flash_decode_scratch_floats(int n_seqs, int nh, int hd, int 
     return (long long)n_seqs * nh * n_chunks * (hd + 2);
 }
 
-SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
-                           const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
-                           int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
-                           int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats, int* counters,
-                           cudaStream_t stream) {
+SP_API int sp_flash_decode_sink(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
+                                const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
+                                int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
+                                int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats, int* counters,
+                                const float* sink, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (check_common(hd, nh, nkv, page_size)) return 1;
     if (nh / nkv > 16) SP_FAIL("flash decode: %d query heads per kv head, at most 16 fit one tile", nh / nkv);
@@ -442,7 +465,7 @@ SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpo
     if (n_seqs > 65535) SP_FAIL("flash decode: %d sequences are beyond this kernel's grid", n_seqs);
     const long long need = sp_flash_decode_scratch_floats(n_seqs, nh, hd, n_chunks);
     if (scratch_floats < need) SP_FAIL("flash decode: scratch holds %lld floats, %lld are needed", scratch_floats, need);
-    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host};
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host, sink};
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)n_seqs * nh * n_chunks * hd;
     dim3 grid(n_chunks, nkv, n_seqs);
@@ -452,11 +475,20 @@ SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpo
     SP_CHECK_LAUNCH("flash_decode");
     if (counters) return 0;                  // the last CTA of every (sequence, kv head) has combined
     if (out_dt == SP_DT_BF16)
-        decode_combine_kernel<__nv_bfloat16><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_chunks, hd);
+        decode_combine_kernel<__nv_bfloat16><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_chunks, hd, sink, nh);
     else
-        decode_combine_kernel<float><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (float*)out, n_chunks, hd);
+        decode_combine_kernel<float><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (float*)out, n_chunks, hd, sink, nh);
     SP_CHECK_LAUNCH("decode_combine");
     return 0;
+}
+
+SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
+                           const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
+                           int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
+                           int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats, int* counters,
+                           cudaStream_t stream) {
+    return sp_flash_decode_sink(q, out, out_dt, kpool, vpool, seq_len, seq_row, page_table, max_pages, page_size, n_seqs, nh,
+                                nkv, hd, window, scale, chunk_tiles, n_chunks, scratch, scratch_floats, counters, nullptr, stream);
 }
 
 // ------------------------------------------------------------------ decode without a caller's scratch

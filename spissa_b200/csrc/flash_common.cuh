@@ -276,6 +276,7 @@ struct PagedKV {
     int max_pages;
     int nkv;
     SpRange rg;                 // what the debug build checks table entries against
+    const float* sink = nullptr;   // [query heads] or null: per head a score that joins the softmax's denominator once, with no key and no value
 };
 
 }  // namespace

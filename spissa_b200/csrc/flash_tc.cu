@@ -61,7 +61,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ seq_start, const int* __restrict__ positions,
                         const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
-                        int n_seqs, int nh, int nkv, float scale_log2, int* status, SpRange rg) {
+                        int n_seqs, int nh, int nkv, float scale_log2, int* status, SpRange rg,
+                        const float* __restrict__ sink) {
     static_assert(HD == 64 || HD == 128, "scores 2 x 64 columns and the output HD columns of 256 in tensor memory");
     using L = Smem<HD>;
     constexpr int KV_STAGES = kv_stages<HD>();
@@ -269,7 +270,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&bar_done), 0, status, 117);
         tc_fence_after();
         if (ok && !(status && *(volatile int*)status != 0)) {
-            const float inv = 1.0f / l;
+            // a sink: one more term in the denominator, with no key and no value (m and the sink's score in log2 units)
+            const float inv = 1.0f / (sink ? l + exp2f(sink[h] * LOG2E - m) : l);
             __nv_bfloat16* dst = out + (size_t)(t0 + row) * nh * HD + (size_t)h * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -342,10 +344,12 @@ SP_API int sp_flash_tc_supported(int hd, int nh, int nkv, int page_size, int win
 
 // q, out: [T, nh*hd] bfloat16; pools: [n_pages, nkv, 64, hd] bfloat16; n_q_tiles = sum over sequences of
 // ceil(new tokens / 128).
-SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
-                               int T, const int* seq_start, const int* positions, const int* seq_row,
-                               const int* page_table, int max_pages, int page_size, int n_seqs, int n_q_tiles, int nh,
-                               int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
+// ``sink`` (float32 per query head, or null): a score that joins every row's denominator once, with no key and no value
+SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
+                                    int T, const int* seq_start, const int* positions, const int* seq_row,
+                                    const int* page_table, int max_pages, int page_size, int n_seqs, int n_q_tiles, int nh,
+                                    int nkv, int hd, int window, float scale, int* status, const float* sink,
+                                    cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
     if (!sp_flash_tc_supported(hd, nh, nkv, page_size, window))
         SP_FAIL("flash_tc: built for head sizes 64 and 128, pages of 64 and no window (got head %d, page %d, window %d)", hd, page_size, window);
@@ -366,7 +370,7 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
         }
         SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<64>, grid, dim3(192), (size_t)Smem<64>::TOTAL, stream,
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status, sp_range_host));
+            scale * LOG2E, status, sp_range_host, sink));
     } else {
         if (!configured[1].done()) {
             cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL);
@@ -375,8 +379,16 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
         }
         SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<128>, grid, dim3(192), (size_t)Smem<128>::TOTAL, stream,
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status, sp_range_host));
+            scale * LOG2E, status, sp_range_host, sink));
     }
     SP_CHECK_LAUNCH("flash_prefill_tc");
     return 0;
+}
+
+SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
+                               int T, const int* seq_start, const int* positions, const int* seq_row,
+                               const int* page_table, int max_pages, int page_size, int n_seqs, int n_q_tiles, int nh,
+                               int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
+    return sp_flash_prefill_tc_sink(q, out, kpool, vpool, n_pages, T, seq_start, positions, seq_row, page_table, max_pages,
+                                    page_size, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, status, nullptr, stream);
 }

@@ -146,3 +146,295 @@ SP_API int sp_headwise_product(const void* a, int a_dt, const void* w, int w_dt,
     SP_CHECK_LAUNCH("headwise_product");
     return 0;
 }
+
+// ============================================================== the attention itself, on tensor cores
+// Queries arrive in the latent's space: q [T][H][RANK] (bfloat16). All heads read the same page rows c_j, and a row
+// is key and value at once, so a tile of LF_KEYS cached rows is fetched into shared memory ONCE and serves both
+// products of a block of LF_ROWS query rows:
+//
+//   S = Q · Cᵀ            (LF_ROWS x LF_KEYS, contraction over RANK)      mma.sync m16n8k16, bfloat16 in, 32-bit out
+//   P = online softmax(S · scale) in 32-bit, rounded to bfloat16 for the second product; the row sums add the rounded
+//       weights, so numerator and denominator agree
+//   O = O · rescale + P · C   (LF_ROWS x RANK, contraction over LF_KEYS)
+//
+// A block's rows are LF_ROWS consecutive tokens of one sequence for one head (a prompt's portion: grid = heads x
+// token tiles) or up to LF_ROWS heads of one token (a decode step: grid = head groups x sequences). Eight warps: for S
+// a warp owns 16 rows x 8 keys over all of RANK; for O it owns RANK/8 columns of all rows (the accumulators are the
+// only large register array: 2 x RANK/64 x 4 floats per thread). Tiles of cached rows arrive by cp.async in two
+// stages. A row sees key j when lo <= j <= its position (lo = position − window + 1 with a window, else 0); a sink
+// adds e^{sink_h} to a row's denominator at the end. Keys are visited in ascending order whatever the block, so a
+// row's sums do not depend on how the tokens were cut into steps beyond the rounding of the rescaling.
+#include "flash_common.cuh"
+
+namespace {
+constexpr int LF_ROWS = 32;
+constexpr int LF_KEYS = 32;
+constexpr int LF_PAGE = 64;
+
+template <int RANK>
+struct LfSmem {
+    static constexpr int LD = RANK + 8;                       // elements per row: 16 bytes of padding spread the banks
+    static constexpr int Q_BYTES = LF_ROWS * LD * 2;
+    static constexpr int K_BYTES = LF_KEYS * LD * 2;
+    static constexpr int S_LD = LF_KEYS + 1;
+    static constexpr int S_BYTES = LF_ROWS * S_LD * 4;
+    static constexpr int P_LD = LF_KEYS + 8;
+    static constexpr int P_BYTES = LF_ROWS * P_LD * 2;
+    static constexpr int META_BYTES = LF_ROWS * 4 * 6;        // rescale, max, sum, position, token, head per row
+    static constexpr int OFF_K = Q_BYTES, OFF_S = OFF_K + 2 * K_BYTES, OFF_P = OFF_S + S_BYTES, OFF_META = OFF_P + P_BYTES;
+    static constexpr int TOTAL = OFF_META + META_BYTES;
+};
+
+struct LfArgs {
+    const __nv_bfloat16* q; __nv_bfloat16* out; const __nv_bfloat16* pool;
+    const int* page_table; const int* seq_row; int max_pages;
+    const int* seq_start; const int* positions; int n_seqs;
+    const float* sink; int H, window; float scale_log2; int decode;
+    SpRange rg;
+};
+
+template <int RANK>
+__global__ void __launch_bounds__(256) latent_flash_kernel(LfArgs a) {
+    using L = LfSmem<RANK>;
+    constexpr int CPW = RANK / 8;                             // output columns per warp
+    static_assert(RANK % 128 == 0, "a warp's columns come in pairs of 8-wide tiles");
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t q_s = smem_u32(smem), k_s = q_s + L::OFF_K, p_s = q_s + L::OFF_P;
+    float* S = (float*)(smem + L::OFF_S);
+    __nv_bfloat16* P = (__nv_bfloat16*)(smem + L::OFF_P);
+    float* fac_s = (float*)(smem + L::OFF_META);
+    float* m_s = fac_s + LF_ROWS;
+    float* l_s = m_s + LF_ROWS;
+    int* pos_s = (int*)(l_s + LF_ROWS);
+    int* tok_s = pos_s + LF_ROWS;
+    int* head_s = tok_s + LF_ROWS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- which rows
+    int b = 0, min_pos = 0, max_pos = 0;
+    if (a.decode) {
+        b = blockIdx.y;
+        const int t = a.seq_start[b], pos = a.positions[t];
+        min_pos = max_pos = pos;
+        if (tid < LF_ROWS) {
+            const int h = blockIdx.x * LF_ROWS + tid;
+            pos_s[tid] = h < a.H ? pos : -1;
+            tok_s[tid] = t;
+            head_s[tid] = h < a.H ? h : 0;
+        }
+    } else {
+        int x = blockIdx.y, first = 0, n_new = 0;
+        for (; b < a.n_seqs; ++b) {
+            first = a.seq_start[b];
+            n_new = a.seq_start[b + 1] - first;
+            const int nt = (n_new + LF_ROWS - 1) / LF_ROWS;
+            if (x < nt) break;
+            x -= nt;
+        }
+        if (b >= a.n_seqs) return;
+        const int t0 = first + x * LF_ROWS, n_rows = min(LF_ROWS, n_new - x * LF_ROWS);
+        const int pos0 = a.positions[t0];
+        min_pos = pos0;
+        max_pos = pos0 + n_rows - 1;
+        if (tid < LF_ROWS) {
+            pos_s[tid] = tid < n_rows ? pos0 + tid : -1;
+            tok_s[tid] = t0 + (tid < n_rows ? tid : 0);
+            head_s[tid] = blockIdx.x;
+        }
+    }
+    __syncthreads();
+    const int* pt = a.page_table + (size_t)sp_checked_row(a.seq_row[b], a.rg) * a.max_pages;
+    const int lo_key = (a.window > 0 && min_pos - a.window + 1 > 0) ? min_pos - a.window + 1 : 0;
+    const int j_lo = lo_key / LF_KEYS, j_hi = max_pos / LF_KEYS;
+
+    // ---- the queries, then the first tile of cached rows
+    constexpr int CHUNKS = RANK / 8;                          // 16-byte pieces per row
+    for (int c = tid; c < LF_ROWS * CHUNKS; c += 256) {
+        const int r = c / CHUNKS, k = c % CHUNKS;
+        const uint32_t d = q_s + (r * L::LD + k * 8) * 2;
+        if (pos_s[r] >= 0) cp_async16(d, a.q + ((size_t)tok_s[r] * a.H + head_s[r]) * RANK + k * 8);
+        else asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(d), "r"(0u) : "memory");
+    }
+    auto load_keys = [&](int jt, int stage) {
+        const int j0 = jt * LF_KEYS;
+        const int page = sp_checked_page(pt[sp_checked_entry(j0 / LF_PAGE, a.max_pages, a.rg)], a.rg);
+        const __nv_bfloat16* src = a.pool + ((size_t)page * LF_PAGE + j0 % LF_PAGE) * RANK;
+        const uint32_t dst = k_s + stage * L::K_BYTES;
+        for (int c = tid; c < LF_KEYS * CHUNKS; c += 256) {
+            const int r = c / CHUNKS, k = c % CHUNKS;
+            cp_async16(dst + (r * L::LD + k * 8) * 2, src + (size_t)r * RANK + k * 8);
+        }
+    };
+    load_keys(j_lo, 0);
+    cp_async_commit();
+
+    float o[2][CPW / 8][4];
+#pragma unroll
+    for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+        for (int nt = 0; nt < CPW / 8; ++nt) o[rt][nt][0] = o[rt][nt][1] = o[rt][nt][2] = o[rt][nt][3] = 0.0f;
+    // the softmax's view: thread -> (row, four neighbouring keys of the tile); the row's eight threads are neighbours in a warp
+    const int srow = tid >> 3, sub = tid & 7;
+    const int spos = pos_s[srow];
+    const int slo = a.window > 0 ? spos - a.window + 1 : 0;
+    float m = -INFINITY, l = 0.0f;
+    const int rt_s = warp & 1, kg = warp >> 1;                // the score product's view: 16 rows x 8 keys per warp
+
+    for (int jt = j_lo; jt <= j_hi; ++jt) {
+        const int stage = (jt - j_lo) & 1;
+        if (jt < j_hi) load_keys(jt + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t kt = k_s + stage * L::K_BYTES;
+        {   // S = Q · Cᵀ
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const uint32_t a_addr = q_s + ((rt_s * 16 + (lane & 15)) * L::LD + (lane >> 4) * 8) * 2;
+            const uint32_t b_addr = kt + ((kg * 8 + (lane & 7)) * L::LD + (lane >> 3) * 8) * 2;
+#pragma unroll 4
+            for (int ks = 0; ks < RANK / 16; ks += 2) {
+                uint32_t af[4], ag[4], b0, b1, b2, b3;
+                ldmatrix_x4(a_addr + ks * 32, af[0], af[1], af[2], af[3]);
+                ldmatrix_x4(a_addr + ks * 32 + 32, ag[0], ag[1], ag[2], ag[3]);
+                ldmatrix_x4(b_addr + ks * 32, b0, b1, b2, b3);
+                mma_bf16(acc, af, b0, b1);
+                mma_bf16(acc, ag, b2, b3);
+            }
+            float* dst = S + (rt_s * 16 + (lane >> 2)) * L::S_LD + kg * 8 + 2 * (lane & 3);
+            dst[0] = acc[0]; dst[1] = acc[1];
+            dst[8 * L::S_LD] = acc[2]; dst[8 * L::S_LD + 1] = acc[3];
+        }
+        __syncthreads();
+        {   // the online softmax of the tile's scores
+            float s[4], tmax = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int j = jt * LF_KEYS + sub * 4 + i;
+                const bool seen = spos >= 0 && j <= spos && j >= slo;
+                s[i] = seen ? S[srow * L::S_LD + sub * 4 + i] * a.scale_log2 : -INFINITY;
+                tmax = fmaxf(tmax, s[i]);
+            }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            const float m_new = fmaxf(m, tmax);
+            float fac = 1.0f, psum = 0.0f;
+            __nv_bfloat16 pb[4];
+            if (m_new == -INFINITY) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pb[i] = __float2bfloat16_rn(0.0f);
+            } else {
+                fac = fast_exp2(m - m_new);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    pb[i] = __float2bfloat16_rn(fast_exp2(s[i] - m_new));
+                    psum += __bfloat162float(pb[i]);
+                }
+            }
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+            l = l * fac + psum;
+            m = m_new;
+            __nv_bfloat162* pd = (__nv_bfloat162*)(P + srow * L::P_LD + sub * 4);
+            pd[0] = __halves2bfloat162(pb[0], pb[1]);
+            pd[1] = __halves2bfloat162(pb[2], pb[3]);
+            if (sub == 0) fac_s[srow] = fac;
+        }
+        __syncthreads();
+        {   // O = O · rescale + P · C
+#pragma unroll
+            for (int rt = 0; rt < 2; ++rt) {
+                const float f0 = fac_s[rt * 16 + (lane >> 2)], f1 = fac_s[rt * 16 + (lane >> 2) + 8];
+#pragma unroll
+                for (int nt = 0; nt < CPW / 8; ++nt) { o[rt][nt][0] *= f0; o[rt][nt][1] *= f0; o[rt][nt][2] *= f1; o[rt][nt][3] *= f1; }
+            }
+#pragma unroll
+            for (int ks = 0; ks < LF_KEYS / 16; ++ks) {
+                uint32_t pa[2][4];
+#pragma unroll
+                for (int rt = 0; rt < 2; ++rt)
+                    ldmatrix_x4(p_s + ((rt * 16 + (lane & 15)) * L::P_LD + ks * 16 + (lane >> 4) * 8) * 2, pa[rt][0], pa[rt][1], pa[rt][2], pa[rt][3]);
+                const uint32_t v_addr = kt + ((ks * 16 + (lane & 15)) * L::LD + warp * CPW + (lane >> 4) * 8) * 2;
+#pragma unroll
+                for (int np = 0; np < CPW / 16; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(v_addr + np * 32, b0, b1, b2, b3);
+#pragma unroll
+                    for (int rt = 0; rt < 2; ++rt) {
+                        mma_bf16(o[rt][2 * np], pa[rt], b0, b1);
+                        mma_bf16(o[rt][2 * np + 1], pa[rt], b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    if (sub == 0) { m_s[srow] = m; l_s[srow] = l; }
+    __syncthreads();
+#pragma unroll
+    for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int r = rt * 16 + (lane >> 2) + hf * 8;
+            if (pos_s[r] < 0) continue;
+            const int h = head_s[r];
+            float mr = m_s[r], lr = l_s[r], f = 1.0f;
+            if (a.sink) {
+                const float sk = a.sink[h] * LOG2E;
+                const float m_all = fmaxf(mr, sk);
+                f = fast_exp2(mr - m_all);
+                lr = lr * f + fast_exp2(sk - m_all);
+            }
+            const float inv = f / lr;
+            __nv_bfloat16* dst = a.out + ((size_t)tok_s[r] * a.H + h) * RANK + warp * CPW + 2 * (lane & 3);
+#pragma unroll
+            for (int nt = 0; nt < CPW / 8; ++nt)
+                *(uint32_t*)(dst + nt * 8) = pack_bf16(o[rt][nt][2 * hf] * inv, o[rt][nt][2 * hf + 1] * inv);
+        }
+}
+
+template <int RANK>
+int launch_latent_flash(dim3 grid, cudaStream_t stream, const LfArgs& a) {
+    static SpPerDevice ok;
+    if (!ok.done()) {
+        cudaError_t e = cudaFuncSetAttribute(latent_flash_kernel<RANK>, cudaFuncAttributeMaxDynamicSharedMemorySize, LfSmem<RANK>::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("latent_flash: cannot reserve %d bytes of shared memory: %s", LfSmem<RANK>::TOTAL, cudaGetErrorString(e));
+        ok.mark();
+    }
+    latent_flash_kernel<RANK><<<grid, 256, LfSmem<RANK>::TOTAL, stream>>>(a);
+    return 0;
+}
+}  // namespace
+
+SP_API int sp_latent_flash_rows() { return LF_ROWS; }
+
+SP_API int sp_latent_flash_supported(int rank, int page_size) {
+    return page_size == LF_PAGE && (rank == 128 || rank == 256 || rank == 384 || rank == 512);
+}
+
+// ``decode``: every sequence brings one token (grid: groups of LF_ROWS heads x sequences); else ``n_q_tiles`` = the sum
+// over sequences of ceil(new tokens / LF_ROWS).
+SP_API int sp_latent_flash(const void* q, void* out, const void* pool, const int* seq_start, const int* positions,
+                           const int* seq_row, const int* page_table, int max_pages, int page_size, int n_seqs,
+                           int n_q_tiles, int decode, int H, int rank, int window, float scale, const float* sink,
+                           cudaStream_t stream) {
+    if (n_seqs <= 0 || (!decode && n_q_tiles <= 0)) return 0;
+    if (!sp_latent_flash_supported(rank, page_size)) SP_FAIL("latent_flash: built for ranks 128, 256, 384, 512 and pages of %d (got %d, %d)", LF_PAGE, rank, page_size);
+    if ((((uintptr_t)q) | ((uintptr_t)out) | ((uintptr_t)pool)) & 15) SP_FAIL("latent_flash: operands must start on a 16-byte boundary");
+    const dim3 grid = decode ? dim3((H + LF_ROWS - 1) / LF_ROWS, n_seqs) : dim3(H, n_q_tiles);
+    if (grid.y > 65535) SP_FAIL("latent_flash: %u rows of blocks are beyond this kernel's grid", grid.y);
+    LfArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pool, page_table, seq_row, max_pages,
+             seq_start, positions, n_seqs, sink, H, window, scale * LOG2E, decode ? 1 : 0, sp_range_host};
+    int rc = 1;
+    switch (rank) {
+        case 128: rc = launch_latent_flash<128>(grid, stream, a); break;
+        case 256: rc = launch_latent_flash<256>(grid, stream, a); break;
+        case 384: rc = launch_latent_flash<384>(grid, stream, a); break;
+        case 512: rc = launch_latent_flash<512>(grid, stream, a); break;
+    }
+    if (rc) return 1;
+    SP_CHECK_LAUNCH("latent_flash");
+    return 0;
+}

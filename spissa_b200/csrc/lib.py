@@ -551,11 +551,6 @@ def flash_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd
     return bool(load("attention").sp_flash_supported(int(hd), int(nh), int(nkv), int(page_size)))
 
 
-def flash_takes_sink() -> bool:
-    """Whether the tensor-core attention kernels take a sink (a score in the denominator that has no key)."""
-    return False
-
-
 def flash_query_tile() -> int:
     """Query rows per CTA of ``flash_prefill``: a step has sum over sequences of ceil(new tokens / this) tiles."""
     return int(load("attention").sp_flash_query_tile())
@@ -570,8 +565,15 @@ def query_tiles(new_counts, tile: int) -> int:
     return sum((int(n) + tile - 1) // tile for n in new_counts)
 
 
-def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale):
-    """Causal attention of a step's tokens (any number per sequence) over the paged cache.
+def _sink_ptr(sink, nh):
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nh or not sink.is_contiguous()):
+        raise KernelError("attention: the sinks are one float32 per query head")
+    return c_void_p(_ptr(sink))
+
+
+def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, sink=None):
+    """Causal attention of a step's tokens (any number per sequence) over the paged cache. ``sink`` (float32 [nh]):
+    per head a score that joins the softmax's denominator once and has no value.
 
     ``seq_start`` [B+1] int32 on the device; ``n_q_tiles`` = sum over sequences of ceil(new tokens /
     ``flash_query_tile()``).
@@ -580,11 +582,11 @@ def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh
     _need_contig(q, out)
     pt = meta.page_table
     _declare_bounds("attention", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
-    _check("attention", lib.sp_flash_prefill(
+    _check("attention", lib.sp_flash_prefill_sink(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)),
         c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles), nh, nkv, hd,
-        int(window or 0), c_float(scale), c_void_p(_stream())))
+        int(window or 0), c_float(scale), _sink_ptr(sink, nh), c_void_p(_stream())))
 
 
 def flash_decode_plan(n_seqs: int, nkv: int, max_len: int, page_size: int = 64) -> tuple:
@@ -610,7 +612,7 @@ def flash_decode_scratch_floats(n_seqs: int, nh: int, hd: int, n_chunks: int) ->
 
 
 def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, scale, chunk_tiles, n_chunks, scratch,
-                 counters=None):
+                 counters=None, sink=None):
     """One query token per sequence: keys split into chunks over CTAs, partial results combined in order.
 
     ``seq_len`` [B] int32: each sequence's length including the query token. ``scratch``: float32,
@@ -625,11 +627,12 @@ def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, sca
     if counters is not None and (counters.dtype != torch.int32 or counters.numel() < n_seqs * nkv):
         raise KernelError("flash_decode: counters must be int32 with a word per (sequence, kv head)")
     _declare_bounds("attention", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
-    _check("attention", lib.sp_flash_decode(
+    _check("attention", lib.sp_flash_decode_sink(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_void_p(_ptr(seq_len)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
         n_seqs, nh, nkv, hd, int(window or 0), c_float(scale), int(chunk_tiles), int(n_chunks),
-        c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_ptr(counters)), c_void_p(_stream())))
+        c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_ptr(counters)), _sink_ptr(sink, nh),
+        c_void_p(_stream())))
     if counters is None:
         launches += 1        # two kernels: the chunks and the combine
 
@@ -688,7 +691,7 @@ def flash_tc_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int,
             and bool(load("flash_tc").sp_flash_tc_supported(int(hd), int(nh), int(nkv), int(page_size), int(window or 0))))
 
 
-def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale):
+def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, sink=None):
     """Causal attention of a step's tokens over the paged cache on the tcgen05 tensor cores.
 
     ``n_q_tiles`` = sum over sequences of ceil(new tokens / ``flash_tc_query_tile()``). S, P and O live in tensor memory.
@@ -697,11 +700,12 @@ def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles,
     _need_contig(q, out, k_pool, v_pool)
     pt = meta.page_table
     _declare_bounds("flash_tc", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
-    _check("flash_tc", lib.sp_flash_prefill_tc(
+    _check("flash_tc", lib.sp_flash_prefill_tc_sink(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_longlong(k_pool.shape[0]), q.shape[0], c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)),
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles),
-        nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_ptr(status_word(q.device))), c_void_p(_stream())))
+        nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_ptr(status_word(q.device))), _sink_ptr(sink, nh),
+        c_void_p(_stream())))
 
 
 # ------------------------------------------------------------------ all layers of a decode step in one kernel
@@ -1251,3 +1255,26 @@ def headwise_product(a, w, out, H, K_, N, w_rows_are_k):
     _check("latent", lib.sp_headwise_product(c_void_p(_ptr(a)), dt_code(a), c_void_p(_ptr(w)), dt_code(w), c_void_p(_ptr(out)),
                                              dt_code(out), a.shape[0], int(H), int(K_), int(N), int(bool(w_rows_are_k)),
                                              c_void_p(_stream())))
+
+
+def latent_flash_supported(rank: int, page_size: int) -> bool:
+    return bool(load("latent").sp_latent_flash_supported(int(rank), int(page_size)))
+
+
+def latent_flash(qc, pool, out, meta, step, H, rank, window, scale, sink=None):
+    """Attention over cached latents on the tensor cores (bfloat16): ``qc`` [T, H·rank] are the queries in the latent's
+    space, ``pool`` [pages, 1, 64, rank] the cached rows (key and value at once), ``out`` [T, H·rank] the weighted sums
+    of rows. Window, sink and scale as for the other attention kernels."""
+    lib = load("latent")
+    _need_contig(qc, out, pool)
+    if qc.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("latent_flash runs on bfloat16 queries and cached rows")
+    pt = meta.page_table
+    _declare_bounds("latent", lib, _pool_pages(meta, pool), _table_rows(meta, pt), qc.device)
+    decode = bool(step.all_single)
+    tiles = 0 if decode else query_tiles(step.host["new_counts"], int(lib.sp_latent_flash_rows()))
+    _check("latent", lib.sp_latent_flash(
+        c_void_p(_ptr(qc)), c_void_p(_ptr(out)), c_void_p(_ptr(pool)), c_void_p(_ptr(step.seq_start)),
+        c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
+        int(step.n_seqs), int(tiles), int(decode), int(H), int(rank), int(window or 0), c_float(scale), _sink_ptr(sink, H),
+        c_void_p(_stream())))

@@ -139,31 +139,36 @@ class GQAAttention(Mixer):
     def attend(self, q, step, cache):
         """The heads' outputs [T, heads·head_dim] for queries ``q`` (positions applied) over the keys and values that
         the cache holds for each token's sequence, the step's own tokens included."""
-        nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        T = q.shape[0]
-        ctx = torch.empty_like(q)
-        if self.sink is not None and not K.flash_takes_sink():
-            K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale, sink=self.sink)
-        elif K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
-            if step.all_single:
-                # the split is made for the length's bucket, not the length: a step run directly and the same step
-                # replayed from a graph (captured for the bucket) then add up in the same order, bit for bit
-                chunk_tiles, n_chunks = K.flash_decode_plan(T, nkv, length_bucket(step.max_len, cache.page_size),
-                                                            cache.page_size)
-                need = K.flash_decode_scratch_floats(T, nh, hd, n_chunks)
-                scratch = torch.empty(need, dtype=torch.float32, device=q.device)
-                K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, self.window,
-                               self.scale, chunk_tiles, n_chunks, scratch,
-                               self.counters if T * nkv <= self.counters.numel() else None)
-            elif T >= 256 and K.flash_tc_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size, self.window):
-                # long prompts: 128-token tiles on the tcgen05 tensor cores (S, P and O in tensor memory)
-                tiles = K.query_tiles(step.host["new_counts"], K.flash_tc_query_tile())
-                K.flash_prefill_tc(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs, tiles,
-                                   nh, nkv, hd, self.window, self.scale)
-            else:
-                tiles = K.query_tiles(step.host["new_counts"], K.flash_query_tile())
-                K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
-                                tiles, nh, nkv, hd, self.window, self.scale)
+        return attend_paged(q, step, cache, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
+                            self.sink, self.counters)
+
+
+def attend_paged(q, step, cache, nh, nkv, hd, window, scale, sink=None, counters=None):
+    """Softmax attention of the step's queries ``q`` [T, nh·hd] over the paged keys and values of ``cache`` (a
+    ``KVLayerView``; key and value rows of one size): the tensor-core kernels where they take the sizes, else the
+    generic one. ``sink``: float32 [nh] or None. ``counters``: the arrival counters of the split-key decode kernel."""
+    T = q.shape[0]
+    ctx = torch.empty_like(q)
+    if K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
+        if step.all_single:
+            # the split is made for the length's bucket, not the length: a step run directly and the same step
+            # replayed from a graph (captured for the bucket) then add up in the same order, bit for bit
+            chunk_tiles, n_chunks = K.flash_decode_plan(T, nkv, length_bucket(step.max_len, cache.page_size),
+                                                        cache.page_size)
+            need = K.flash_decode_scratch_floats(T, nh, hd, n_chunks)
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+            K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, window,
+                           scale, chunk_tiles, n_chunks, scratch,
+                           counters if counters is not None and T * nkv <= counters.numel() else None, sink=sink)
+        elif T >= 256 and K.flash_tc_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size, window):
+            # long prompts: 128-token tiles on the tcgen05 tensor cores (S, P and O in tensor memory)
+            tiles = K.query_tiles(step.host["new_counts"], K.flash_tc_query_tile())
+            K.flash_prefill_tc(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs, tiles,
+                               nh, nkv, hd, window, scale, sink=sink)
         else:
-            K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale, sink=self.sink)
-        return ctx
+            tiles = K.query_tiles(step.host["new_counts"], K.flash_query_tile())
+            K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
+                            tiles, nh, nkv, hd, window, scale, sink=sink)
+    else:
+        K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, window, scale, sink=sink)
+    return ctx

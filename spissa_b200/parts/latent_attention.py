@@ -20,6 +20,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib as K
+from .attention import attend_paged
 from .base import KVCacheRequest, Mixer, WeightSpec
 from .linear import Linear
 from .registry import register_part
@@ -32,6 +33,7 @@ _UNSET = object()
 class LatentAttention(Mixer):
     graph_safe = True
     kernel_modules = ("latent",)
+    kernel_modules_bf16 = ("attention",)
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, v_head_dim: int, q_rank: int, kv_rank: int,
                  scale: float, eps: float, window=None, cache_window=_UNSET, sink: bool = True, shares_latent: bool = False,
@@ -78,6 +80,8 @@ class LatentAttention(Mixer):
         self.uv = tensors[n["uv"]].contiguous()            # [H·vdim, rank]
         self.o = Linear(tensors[n["o"]])
         self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None     # a score: 32-bit
+        # arrival counters of the split-key decode attention; the kernel returns them to zero
+        self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
 
     def forward(self, x, step, cache, residual):
         H, d, vd, qr, r = self.num_heads, self.head_dim, self.v_head_dim, self.q_rank, self.kv_rank
@@ -104,8 +108,12 @@ class LatentAttention(Mixer):
             self.o(ctx, out=residual, accumulate=True)
 
     def attend(self, qc, step, cache):
-        """Σ_j p_h(i, j) c_j for queries already in the latent's space: [T, heads·rank]."""
+        """Σ_j p_h(i, j) c_j for queries already in the latent's space: [T, heads·rank]. In bfloat16 the kernel that
+        fetches a tile of cached rows once for both products where it is built for the rank; else the cache is read as
+        one key/value head of size ``rank`` whose value pool is its key pool, by the grouped-query kernels."""
         H, r = self.num_heads, self.kv_rank
-        mix = torch.empty_like(qc)
-        K.attention_generic(qc, cache.k_pool, cache.k_pool, mix, cache, H, 1, r, self.window, self.scale, sink=self.sink)
-        return mix
+        if qc.dtype == torch.bfloat16 and cache.k_pool.dtype == torch.bfloat16 and K.latent_flash_supported(r, cache.page_size):
+            mix = torch.empty_like(qc)
+            K.latent_flash(qc, cache.k_pool, mix, cache, step, H, r, self.window, self.scale, self.sink)
+            return mix
+        return attend_paged(qc, step, cache, H, 1, r, self.window, self.scale, self.sink, self.counters)
