@@ -4,6 +4,7 @@
                     [--context T] [--profile-phases]
     python bench.py --design duzinex [--design-sizes 1k,2k,4k]      (the Duzinex decoder beside Llama at equal sizes)
     python bench.py --design gozatar [--design-sizes 1k,2k,4k]      (the Gozatar decoder likewise)
+    python bench.py --design kugirax [--design-sizes 1k,2k,4k]      (the Kugirax decoder likewise)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 from prompts of
 about 2,048 tokens in a cache of 4,096 tokens per sequence, timed on the device with CUDA
@@ -230,6 +231,38 @@ def gozatar_config(size: dict, goz: dict, window: int = DESIGN_WINDOW) -> dict:
     return dict(architecture="Gozatar", vocab=DESIGN_VOCAB, width=W, streams=2, norm=dict(eps=1e-6), layers=layers)
 
 
+# --design kugirax: eight layers with one norm each; six of them a grouped-query attention whose q and k pass a
+# convolution of four taps, whose values are the keys, fully rotated, with one added to the softmax's denominator; layers
+# 2 and 6 an attention through a cached latent (window 1,024, a sink per head), layer 6 reading the rows layer 2 cached.
+# Even layers have a dense feed-forward of ``ff``, odd ones 32 experts of ff/4 of which a token uses 4 plus a gated
+# shared expert of ff/4.
+KUGIRAX_SIZES = {
+    # (attention: heads, kv heads, dim), (latent: heads, dim, vdim, q_rank, kv_rank)
+    "1k": dict(att=(8, 2, 128), lat=(8, 128, 128, 512, 256)),
+    "2k": dict(att=(16, 4, 128), lat=(16, 128, 128, 768, 256)),
+    "4k": dict(att=(32, 8, 128), lat=(32, 128, 128, 1536, 512)),
+}
+KUGIRAX_LAYERS, KUGIRAX_LATENT = 8, (2, 6)
+
+
+def kugirax_config(size: dict, kx: dict, window: int = DESIGN_WINDOW) -> dict:
+    W, ff = size["width"], size["ff"]
+    h, g, d = kx["att"]
+    lh, ld, lvd, qr, r = kx["lat"]
+    att = dict(heads=h, kv_heads=g, dim=d, vdim=d, conv=4, scale=d ** -0.5, rot=dict(dims=d, base=10000.0))
+    lat = dict(heads=lh, dim=ld, vdim=lvd, q_rank=qr, kv_rank=r, scale=ld ** -0.5, mask=dict(size=window))
+    moe = dict(kind="moe", expert=dict(ff=ff // 4), shared=dict(ff=ff // 4), router=dict(experts=32, top=4, scale=1.5))
+    layers = []
+    for i in range(KUGIRAX_LAYERS):
+        mlp = dict(kind="dense", ff=ff) if i % 2 == 0 else moe
+        if i in KUGIRAX_LATENT:
+            m = dict(lat, kv_from=KUGIRAX_LATENT[0]) if i != KUGIRAX_LATENT[0] else lat
+            layers.append(dict(type="latent_attention", mixer=m, mlp=mlp))
+        else:
+            layers.append(dict(type="attention", mixer=att, mlp=mlp))
+    return dict(architecture="Kugirax", vocab=DESIGN_VOCAB, width=W, norm=dict(eps=1e-6), logit_softcap=30.0, layers=layers)
+
+
 def design_compare(args) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8 behind such prompts) of the Duzinex decoder and of the
     Llama decoder with the same width, feed-forward size and number of layer runs; per-phase device times of both
@@ -248,7 +281,8 @@ def design_compare(args) -> int:
     names = [n for n in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES) if n in DESIGN_SIZES]
     for name in names:
         size = DESIGN_SIZES[name]
-        dz = duzinex_config(size) if design == "duzinex" else gozatar_config(size, GOZATAR_SIZES[name])
+        dz = (duzinex_config(size) if design == "duzinex" else gozatar_config(size, GOZATAR_SIZES[name]) if design == "gozatar"
+              else kugirax_config(size, KUGIRAX_SIZES[name]))
         runs = len(config_from_dict(dz).to_spec().schedule)
         row = {}
         for label, cfg_dict in ((design, dz), ("llama", llama_config_like(size, runs))):
@@ -323,7 +357,8 @@ def design_compare(args) -> int:
             torch.cuda.empty_cache()
         eb = 4 if args.dtype == "float32" else 2
         row["rooflines"] = (design_rooflines(size, row, T, B, peaks, eb) if design == "duzinex"
-                            else gozatar_rooflines(size, GOZATAR_SIZES[name], row, T, peaks, eb))
+                            else gozatar_rooflines(size, GOZATAR_SIZES[name], row, T, peaks, eb) if design == "gozatar"
+                            else kugirax_rooflines(size, KUGIRAX_SIZES[name], row, T, peaks, eb))
         out["sizes"][name] = row
     print(json.dumps(out))
     return 0
@@ -333,7 +368,9 @@ def _linears(model):
     found = []
 
     def walk(p):
-        for v in vars(p).values():
+        for k, v in vars(p).items():
+            if k.endswith("_fold"):
+                continue                                  # maps multiplied out for prompt steps: decode steps do not read them
             if hasattr(v, "weight") and hasattr(v, "out_features"):
                 found.append(v)
             elif hasattr(v, "plain") and hasattr(v.plain, "out_features"):
@@ -409,6 +446,46 @@ def gozatar_rooflines(size, goz, row, T, peaks, eb) -> dict:
     out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
     act_ms = gz.get("activation_ms")
     out["activations (hbm)"] = dict(ms=act_ms, frac=frac((2 * T * ff + n_moe * T * 3 * (ff // 4)) * (4.0 + eb) * 1.0, bw, act_ms))
+    return out
+
+
+def kugirax_rooflines(size, kx, row, T, peaks, eb) -> dict:
+    """The same for the Kugirax decoder's kernel groups of a prompt step (sums over its eight layers)."""
+    W, ff = size["width"], size["ff"]
+    h, g, d = kx["att"]
+    lh, ld, lvd, qr, r = kx["lat"]
+    nh, nkv, hd = size["llama"]
+    kz, ll = row["kugirax"]["prefill_phases_ms"], row["llama"]["prefill_phases_ms"]
+    tf, bw = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    n_lat = len(KUGIRAX_LATENT)
+    n_att, n_moe = KUGIRAX_LAYERS - n_lat, KUGIRAX_LAYERS // 2
+    win = min(T, DESIGN_WINDOW)
+    pairs = T * win - win * (win - 1) / 2
+    frac = lambda work, peak, ms: round(work / (ms * 1e-3) / peak, 4) if ms else None
+    out = {}
+    out["attention with a unit sink (tensor)"] = dict(ms=kz.get("attention_ms"),
+                                                      frac=frac(n_att * 4.0 * (T * (T + 1) / 2) * d * h, tf, kz.get("attention_ms")))
+    ll_att, ll_runs = ll.get("attention_ms"), row["llama"]["layer_runs"]
+    out["llama attention (tensor)"] = dict(ms=ll_att, frac=frac(ll_runs * 4.0 * (T * (T + 1) / 2) * hd * nh, tf, ll_att))
+    # over latents: per (query, visible row) pair and head 2·rank FLOPs for the score and 2·rank for the weighted sum
+    out["latent attention (tensor)"] = dict(ms=kz.get("latent_attention_ms"),
+                                            frac=frac(n_lat * 4.0 * pairs * r * lh, tf, kz.get("latent_attention_ms")))
+    # the same attention on expanded keys and values would do 2·dim + 2·vdim per pair: the least any form does
+    out["latent attention, expanded count (tensor)"] = dict(ms=kz.get("latent_attention_ms"),
+                                                            frac=frac(n_lat * 2.0 * pairs * (ld + lvd) * lh, tf, kz.get("latent_attention_ms")))
+    hp = (kz.get("query_into_latent_space_ms") or 0) + (kz.get("value_expansion_ms") or 0)
+    out["per-head products (tensor)"] = dict(ms=hp, frac=frac(n_lat * T * lh * 2.0 * r * (ld + lvd), tf, hp))
+    out["latent norms+append (hbm)"] = dict(ms=kz.get("latent_norm+append_ms"),
+                                            frac=frac((T * (qr + r) * 4.0 + T * (qr + r) * eb) + T * qr * (4.0 + eb), bw,
+                                                      kz.get("latent_norm+append_ms")))
+    out["experts (tensor)"] = dict(ms=kz.get("experts_ms"), frac=frac(n_moe * T * 4 * 3 * 2.0 * W * (ff // 4), tf, kz.get("experts_ms")))
+    ll_ff = sum(v for k, v in ll.items() if "gate_projection" in k or "down_projection" in k)
+    out["llama feed-forward (tensor)"] = dict(ms=ll_ff, frac=frac(ll_runs * T * 3 * 2.0 * W * ff, tf, ll_ff))
+    C = (h + g) * d
+    out["conv+rotary+store (hbm)"] = dict(ms=kz.get("conv+rotary+kv_append_ms"),
+                                          frac=frac(n_att * T * (C * 4.0 + (h + 2 * g) * d * eb), bw, kz.get("conv+rotary+kv_append_ms")))
+    out["norm (hbm)"] = dict(ms=kz.get("input_norm_ms"), frac=frac(KUGIRAX_LAYERS * T * W * (4.0 + eb), bw, kz.get("input_norm_ms")))
+    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
     return out
 
 
@@ -833,7 +910,7 @@ def main() -> int:
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
                          "gemv_down|gemv_head|diff_flash|diff_decode|retention_chunks|retention_step|mingru_chunks|polynorm|token_shift|gla_chunks|gla_step|moe_experts|moe_experts_b8|streams_norm|conv_qk_store|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
-    ap.add_argument("--design", default=None, choices=["duzinex", "gozatar"],
+    ap.add_argument("--design", default=None, choices=["duzinex", "gozatar", "kugirax"],
                     help="measure this design beside the Llama decoder at equal layer sizes instead of the headline workload")
     ap.add_argument("--design-sizes", default="", dest="design_sizes", help="which of 1k,2k,4k (default: all)")
     ap.add_argument("--reps", type=int, default=20)

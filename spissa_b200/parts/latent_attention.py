@@ -14,6 +14,15 @@ latents is expanded once per token. A layer built with ``shares_latent`` has no 
 it reads the rows another layer cached (a run with ``cache.writes`` False), with its own U_k, U_v, queries, window
 and sinks. ``cache_window``: the window the cache keeps rows for when readers with other windows share it (None with
 ``window`` set: this layer's own).
+
+Two ways to carry the queries in and the sums out. Few tokens (decode steps) and the 32-bit mode take the small
+per-head products as they stand: q = U_q c_q, then U_k,hᵀ q_h; U_v,h (Σ p c), then W_o. Prompt portions in bfloat16
+take the same maps multiplied out once when the weights are bound,
+
+    A = stack_h(U_k,hᵀ U_q,h)   [heads·rank, q_rank]        B = concat_h(W_o[:, h] U_v,h)   [hidden, heads·rank]
+
+(products in 32-bit, rounded once to bfloat16), so that both are plain matrix products on the tile kernel: more FLOPs
+than the small products, but at the tensor cores' rate instead of a per-head loop.
 """
 from __future__ import annotations
 
@@ -27,6 +36,8 @@ from .registry import register_part
 from ..phases import phase
 
 _UNSET = object()
+FOLDED_FROM_TOKENS = 64      # steps of more tokens than this take the multiplied-out maps (bfloat16): below, the weights'
+#                              bytes decide, and the small products read a third of them
 
 
 @register_part("mixer", "latent_attention")
@@ -80,6 +91,13 @@ class LatentAttention(Mixer):
         self.uv = tensors[n["uv"]].contiguous()            # [H·vdim, rank]
         self.o = Linear(tensors[n["o"]])
         self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None     # a score: 32-bit
+        self.q_fold = self.o_fold = None
+        if rt.act_dtype == torch.bfloat16 and all(w.dtype == torch.bfloat16 for w in (self.uk, self.uv, self.uq.weight, self.o.weight)):
+            H, d, vd, qr, r = self.num_heads, self.head_dim, self.v_head_dim, self.q_rank, self.kv_rank
+            uk, uq = self.uk.float().view(H, d, r), self.uq.weight.float().view(H, d, qr)
+            self.q_fold = Linear(torch.bmm(uk.transpose(1, 2), uq).reshape(H * r, qr).to(torch.bfloat16))
+            wo, uv = self.o.weight.float().view(-1, H, vd).permute(1, 0, 2), self.uv.float().view(H, vd, r)
+            self.o_fold = Linear(torch.bmm(wo, uv).permute(1, 0, 2).reshape(-1, H * r).to(torch.bfloat16))
         # arrival counters of the split-key decode attention; the kernel returns them to zero
         self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
 
@@ -95,12 +113,22 @@ class LatentAttention(Mixer):
             cq = torch.empty(T, qr, dtype=act, device=dev)
             K.latent_norm_store(proj, qr, r, self.wq_norm, self.wc_norm if writes else None, self.eps, cq,
                                 cache.k_pool if writes else None, cache)
-        with phase("q_projection_ms"):
-            q = self.uq(cq)
-            qc = torch.empty(T, H * r, dtype=act, device=dev)
-            K.headwise_product(q, self.uk, qc, H, d, r, w_rows_are_k=True)                # U_k,hᵀ q_h
-        with phase("attention_ms"):
+        folded = self.q_fold is not None and T > FOLDED_FROM_TOKENS
+        if folded:
+            with phase("q_projection_ms"):
+                qc = self.q_fold(cq)                                                      # (U_k,hᵀ U_q,h) c_q
+        else:
+            with phase("q_projection_ms"):
+                q = self.uq(cq)
+            with phase("query_into_latent_space_ms"):
+                qc = torch.empty(T, H * r, dtype=act, device=dev)
+                K.headwise_product(q, self.uk, qc, H, d, r, w_rows_are_k=True)            # U_k,hᵀ q_h
+        with phase("latent_attention_ms"):
             mix = self.attend(qc, step, cache)
+        if folded:
+            with phase("o_projection+attention_residual_ms"):
+                self.o_fold(mix, out=residual, accumulate=True)                           # (W_o,h U_v,h) Σ p c
+            return
         with phase("value_expansion_ms"):
             ctx = torch.empty(T, H * vd, dtype=act, device=dev)
             K.headwise_product(mix, self.uv, ctx, H, r, vd, w_rows_are_k=False)           # U_v,h (Σ p c)
