@@ -848,6 +848,56 @@ def kernel_case(name: str, reps: int) -> int:
                                    seq_slot=i32([0]), positions=step.positions, token_seq=step.token_seq)
             run = lambda i: K.conv_qk_store(qkvs[i % 4], conv, 4, state, q, kp, vp, meta, step, inv_freq, nh, nkv, d, d, d // 2, 1e-6)
             bytes_ = T * C * (4 + 2.0)
+    elif name in ("latent_flash", "latent_flash_b8", "latent_window_as_gqa", "latent_norm_store", "headwise_b8", "headwise"):
+        # the Kugirax latent attention at the 2k size of --design (16 heads over rows of 256, a window of 1,024, sinks)
+        LH, r, d, qr, win = 16, 256, 128, 768, 1024
+        B = 8 if name.endswith("_b8") else 1
+        n_new = 1 if B > 1 else T
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        ar = torch.arange(B, dtype=torch.int32, device=dev)
+        pos = (torch.arange(n_new, dtype=torch.int32, device=dev) + (T - n_new)).repeat(B)
+        step = SimpleNamespace(seq_start=i32([n_new * b for b in range(B + 1)]), seq_slot=ar, token_seq=ar.repeat_interleave(n_new),
+                               n_seqs=B, positions=pos, all_single=n_new == 1, max_new=n_new, max_len=T,
+                               seq_len=i32([T] * B), host=dict(new_counts=[n_new] * B))
+        pages = B * (T // 64)
+        n_buf = 24 if B > 1 else 1                             # a decode step reads 8 x 1,024 rows of 512 bytes: rotate the pools
+        pools = [rnd(pages, 1, 64, r) for _ in range(n_buf)]
+        meta = SimpleNamespace(page_table=torch.arange(pages, dtype=torch.int32, device=dev).view(B, T // 64), page_size=64,
+                               seq_slot=ar, positions=pos, token_seq=step.token_seq)
+        sink = torch.zeros(LH, device=dev)
+        rows = B * n_new
+        pairs = B * (T * win - win * (win - 1) / 2) if B == 1 else B * win
+        if name.startswith("latent_flash"):
+            q = rnd(rows, LH * r)
+            out = torch.empty_like(q)
+            run = lambda i: K.latent_flash(q, pools[i % n_buf], out, meta, step, LH, r, win, d ** -0.5, sink, max_len=T if B > 1 else None)
+            if B > 1:
+                bytes_ = B * win * r * 2.0
+            else:
+                flops = 4.0 * pairs * r * LH
+        elif name == "latent_window_as_gqa":
+            # the grouped-query kernel of the same window on expanded heads of 128 (what a cache of keys and values would run)
+            kp, vp = rnd(pages, 4, 64, d), rnd(pages, 4, 64, d)
+            q = rnd(rows, LH * d)
+            out = torch.empty_like(q)
+            run = lambda i: K.flash_prefill(q, kp, vp, out, meta, step.seq_start, 1, T // 64, LH, 4, d, win, d ** -0.5, sink=sink)
+            flops = 4.0 * pairs * d * LH
+        elif name == "latent_norm_store":
+            projs = [torch.randn(T, qr + r, device=dev) for _ in range(4)]
+            wq, wc = rnd(qr), rnd(r)
+            cq = torch.empty(T, qr, dtype=bf, device=dev)
+            run = lambda i: K.latent_norm_store(projs[i % 4], qr, r, wq, wc, 1e-6, cq, pools[0], meta)
+            bytes_ = T * (qr + r) * (4 + 2.0)
+        else:
+            n_w = 64 if B > 1 else 1
+            uks = [rnd(LH * d, r) for _ in range(n_w)]
+            a = rnd(rows, LH * d)
+            out = torch.empty(rows, LH * r, dtype=bf, device=dev)
+            run = lambda i: K.headwise_product(a, uks[i % n_w], out, LH, d, r, w_rows_are_k=True)
+            if B > 1:
+                bytes_ = LH * d * r * 2.0
+            else:
+                flops = rows * LH * 2.0 * d * r
     elif name in ("sample_b8", "sample_b64", "argmax_b8"):
         # the sampler on rows of 128,256 logits (standard deviation 4 after the temperature): temperature 0.8, top-p 0.95
         B = 64 if name.endswith("b64") else 8

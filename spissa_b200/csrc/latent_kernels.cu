@@ -75,11 +75,12 @@ SP_API int sp_latent_norm_store(const float* proj, int ld, const void* wq, const
 // out[t][h][n] = Σ_k a[t][h][k] · W_h[k][n]. ``w`` holds the heads' matrices one after another, either as rows of k
 // (w[h][k][n], ``w_rows_are_k``) or as rows of n (w[h][n][k]): a slice [h·N … (h+1)·N) of rows of a matrix stored
 // [out, in]. A block takes HW_TT tokens x HW_TN outputs of one head; a and W pass through shared memory in blocks
-// of HW_TK of k; a thread owns one output column for all the block's tokens and adds over k in ascending order.
-#define HW_TT 32
+// of HW_TK of k; a thread owns one output column for all the block's tokens and adds over k in ascending order
+// (so a token's result does not depend on the block it falls into, nor on HW_TT). Steps of a few tokens (decoding)
+// take blocks of 8 tokens: a quarter of the multiply-adds, which are all that such a block waits for.
 #define HW_TN 128
 #define HW_TK 32
-template <typename TA, typename TW, typename TO>
+template <typename TA, typename TW, typename TO, int HW_TT>
 __global__ void __launch_bounds__(HW_TN)
 headwise_product_kernel(const TA* __restrict__ a, const TW* __restrict__ w, TO* __restrict__ out, int T, int H, int K, int N,
                         int w_rows_are_k) {
@@ -98,12 +99,14 @@ headwise_product_kernel(const TA* __restrict__ a, const TW* __restrict__ w, TO* 
             As[tt][kk] = (t < T && k < K) ? sp_ld(a, ((size_t)t * H + h) * K + k) : 0.0f;
         }
         if (w_rows_are_k) {
+#pragma unroll 16
             for (int e = tid; e < HW_TK * HW_TN; e += HW_TN) {
                 const int kk = e / HW_TN, nn = e % HW_TN;
                 const int k = k0 + kk, n = n0 + nn;
                 Ws[kk][nn] = (k < K && n < N) ? sp_ld(wh, (size_t)k * N + n) : 0.0f;
             }
         } else {
+#pragma unroll 16
             for (int e = tid; e < HW_TK * HW_TN; e += HW_TN) {
                 const int nn = e / HW_TK, kk = e % HW_TK;
                 const int k = k0 + kk, n = n0 + nn;
@@ -132,9 +135,14 @@ SP_API int sp_headwise_product(const void* a, int a_dt, const void* w, int w_dt,
                                int N, int w_rows_are_k, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || K <= 0 || N <= 0) SP_FAIL("headwise_product: sizes %d x %d x %d", H, K, N);
-    const dim3 grid((T + HW_TT - 1) / HW_TT, H, (N + HW_TN - 1) / HW_TN);
+    const int tt = T <= 16 ? 8 : 32;
+    const dim3 grid((T + tt - 1) / tt, H, (N + HW_TN - 1) / HW_TN);
     if (grid.y > 65535 || grid.z > 65535) SP_FAIL("headwise_product: %d heads or %d outputs are too many for one launch", H, N);
-#define HW_LAUNCH(TA, TW, TO) headwise_product_kernel<TA, TW, TO><<<grid, HW_TN, 0, stream>>>((const TA*)a, (const TW*)w, (TO*)out, T, H, K, N, w_rows_are_k)
+#define HW_LAUNCH(TA, TW, TO)                                                                                                  \
+    do {                                                                                                                       \
+        if (tt == 8) headwise_product_kernel<TA, TW, TO, 8><<<grid, HW_TN, 0, stream>>>((const TA*)a, (const TW*)w, (TO*)out, T, H, K, N, w_rows_are_k); \
+        else headwise_product_kernel<TA, TW, TO, 32><<<grid, HW_TN, 0, stream>>>((const TA*)a, (const TW*)w, (TO*)out, T, H, K, N, w_rows_are_k); \
+    } while (0)
     typedef __nv_bfloat16 bf;
     if (a_dt == SP_DT_F32 && w_dt == SP_DT_F32 && out_dt == SP_DT_F32) HW_LAUNCH(float, float, float);
     else if (a_dt == SP_DT_BF16 && w_dt == SP_DT_BF16 && out_dt == SP_DT_BF16) HW_LAUNCH(bf, bf, bf);
@@ -163,7 +171,10 @@ SP_API int sp_headwise_product(const void* a, int a_dt, const void* w, int w_dt,
 // only large register array: 2 x RANK/64 x 4 floats per thread). Tiles of cached rows arrive by cp.async in two
 // stages. A row sees key j when lo <= j <= its position (lo = position − window + 1 with a window, else 0); a sink
 // adds e^{sink_h} to a row's denominator at the end. Keys are visited in ascending order whatever the block, so a
-// row's sums do not depend on how the tokens were cut into steps beyond the rounding of the rescaling.
+// row's sums do not depend on how the tokens were cut into steps beyond the rounding of the rescaling. A decode step
+// has few rows and many keys: its visible keys are shared out over blockIdx.z (as many blocks as fill the SMs, at
+// least 128 keys each), every share leaves its unnormalised sums with their (max, sum) in scratch, and a second
+// kernel adds the shares in ascending order of keys and brings the sink in once.
 #include "flash_common.cuh"
 
 namespace {
@@ -191,6 +202,9 @@ struct LfArgs {
     const int* seq_start; const int* positions; int n_seqs;
     const float* sink; int H, window; float scale_log2; int decode;
     SpRange rg;
+    // a decode step's keys split over blockIdx.z: ``chunk_tiles`` key tiles per block, unnormalised partial sums
+    // [sequence][head][chunk][RANK] and their (max, sum) pairs to scratch, combined by ``latent_combine_kernel``
+    int n_chunks, chunk_tiles; float* part_o; float* part_ml;
 };
 
 template <int RANK>
@@ -245,7 +259,20 @@ __global__ void __launch_bounds__(256) latent_flash_kernel(LfArgs a) {
     __syncthreads();
     const int* pt = a.page_table + (size_t)sp_checked_row(a.seq_row[b], a.rg) * a.max_pages;
     const int lo_key = (a.window > 0 && min_pos - a.window + 1 > 0) ? min_pos - a.window + 1 : 0;
-    const int j_lo = lo_key / LF_KEYS, j_hi = max_pos / LF_KEYS;
+    int j_lo = lo_key / LF_KEYS, j_hi = max_pos / LF_KEYS;
+    const bool split = a.n_chunks > 1;
+    if (split) {                                              // this block's share of the key tiles, counted from the first visible one
+        j_lo += blockIdx.z * a.chunk_tiles;
+        j_hi = min(j_hi, j_lo + a.chunk_tiles - 1);
+        if (j_lo > j_hi) {                                    // beyond the row's keys: an empty share
+            if (tid < LF_ROWS && pos_s[tid] >= 0) {
+                float* ml = a.part_ml + (((size_t)b * a.H + head_s[tid]) * a.n_chunks + blockIdx.z) * 2;
+                ml[0] = -INFINITY;
+                ml[1] = 0.0f;
+            }
+            return;
+        }
+    }
 
     // ---- the queries, then the first tile of cached rows
     constexpr int CHUNKS = RANK / 8;                          // 16-byte pieces per row
@@ -373,6 +400,25 @@ __global__ void __launch_bounds__(256) latent_flash_kernel(LfArgs a) {
     cp_async_wait<0>();
     if (sub == 0) { m_s[srow] = m; l_s[srow] = l; }
     __syncthreads();
+    if (split) {
+        if (tid < LF_ROWS && pos_s[tid] >= 0) {
+            float* ml = a.part_ml + (((size_t)b * a.H + head_s[tid]) * a.n_chunks + blockIdx.z) * 2;
+            ml[0] = m_s[tid];
+            ml[1] = l_s[tid];
+        }
+#pragma unroll
+        for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int r = rt * 16 + (lane >> 2) + hf * 8;
+                if (pos_s[r] < 0) continue;
+                float* dst = a.part_o + (((size_t)b * a.H + head_s[r]) * a.n_chunks + blockIdx.z) * RANK + warp * CPW + 2 * (lane & 3);
+#pragma unroll
+                for (int nt = 0; nt < CPW / 8; ++nt)
+                    *(float2*)(dst + nt * 8) = make_float2(o[rt][nt][2 * hf], o[rt][nt][2 * hf + 1]);
+            }
+        return;
+    }
 #pragma unroll
     for (int rt = 0; rt < 2; ++rt)
 #pragma unroll
@@ -393,6 +439,40 @@ __global__ void __launch_bounds__(256) latent_flash_kernel(LfArgs a) {
             for (int nt = 0; nt < CPW / 8; ++nt)
                 *(uint32_t*)(dst + nt * 8) = pack_bf16(o[rt][nt][2 * hf] * inv, o[rt][nt][2 * hf + 1] * inv);
         }
+}
+
+// The shares of one (sequence, head) in ascending order of keys: out = Σ_c O_c 2^{m_c − M} / (Σ_c l_c 2^{m_c − M} + 2^{sink − M}).
+__global__ void __launch_bounds__(128) latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                             __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_start,
+                                                             const float* __restrict__ sink, int H, int rank, int n_chunks) {
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    const float* ml = part_ml + (size_t)blockIdx.x * n_chunks * 2;
+    float M = sink ? sink[h] * LOG2E : -INFINITY;
+    for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, ml[2 * c]);
+    float l = sink ? exp2f(sink[h] * LOG2E - M) : 0.0f;
+    for (int c = 0; c < n_chunks; ++c)
+        if (ml[2 * c + 1] > 0.0f) l += ml[2 * c + 1] * exp2f(ml[2 * c] - M);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    const float* po = part_o + (size_t)blockIdx.x * n_chunks * rank;
+    __nv_bfloat16* dst = out + ((size_t)seq_start[b] * H + h) * rank;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int c = 0; c < n_chunks; ++c)
+            if (ml[2 * c + 1] > 0.0f) acc = fmaf(po[(size_t)c * rank + i], exp2f(ml[2 * c] - M), acc);
+        dst[i] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// How a decode step's keys are shared out: enough blocks for the SMs, at least four tiles (128 keys) each.
+void latent_flash_plan(int n_seqs, int H, int window, int max_len, int* chunk_tiles, int* n_chunks) {
+    const int span = window > 0 && window < max_len ? window : max_len;
+    const int tiles = (span + LF_KEYS - 1) / LF_KEYS + 1;                   // a window may straddle one more tile
+    const int blocks = n_seqs * ((H + LF_ROWS - 1) / LF_ROWS);
+    int want = (2 * 148 + blocks - 1) / blocks;
+    if (want > tiles / 4) want = tiles / 4;
+    if (want < 1) want = 1;
+    *chunk_tiles = (tiles + want - 1) / want;
+    *n_chunks = (tiles + *chunk_tiles - 1) / *chunk_tiles;
 }
 
 template <int RANK>
@@ -416,17 +496,33 @@ SP_API int sp_latent_flash_supported(int rank, int page_size) {
 
 // ``decode``: every sequence brings one token (grid: groups of LF_ROWS heads x sequences); else ``n_q_tiles`` = the sum
 // over sequences of ceil(new tokens / LF_ROWS).
+// Floats of scratch that a decode step of ``n_seqs`` sequences no longer than ``max_len`` needs (0: its keys are not split).
+SP_API long long sp_latent_flash_scratch_floats(int n_seqs, int H, int rank, int window, int max_len) {
+    int ct, nc;
+    latent_flash_plan(n_seqs, H, window, max_len, &ct, &nc);
+    return nc > 1 ? (long long)n_seqs * H * nc * (rank + 2) : 0;
+}
+
 SP_API int sp_latent_flash(const void* q, void* out, const void* pool, const int* seq_start, const int* positions,
                            const int* seq_row, const int* page_table, int max_pages, int page_size, int n_seqs,
                            int n_q_tiles, int decode, int H, int rank, int window, float scale, const float* sink,
-                           cudaStream_t stream) {
+                           int max_len, float* scratch, long long scratch_floats, cudaStream_t stream) {
     if (n_seqs <= 0 || (!decode && n_q_tiles <= 0)) return 0;
     if (!sp_latent_flash_supported(rank, page_size)) SP_FAIL("latent_flash: built for ranks 128, 256, 384, 512 and pages of %d (got %d, %d)", LF_PAGE, rank, page_size);
     if ((((uintptr_t)q) | ((uintptr_t)out) | ((uintptr_t)pool)) & 15) SP_FAIL("latent_flash: operands must start on a 16-byte boundary");
-    const dim3 grid = decode ? dim3((H + LF_ROWS - 1) / LF_ROWS, n_seqs) : dim3(H, n_q_tiles);
+    int chunk_tiles = 0, n_chunks = 1;
+    if (decode && scratch && max_len > 0) {
+        latent_flash_plan(n_seqs, H, window, max_len, &chunk_tiles, &n_chunks);
+        if (n_chunks > 1 && scratch_floats < (long long)n_seqs * H * n_chunks * (rank + 2))
+            SP_FAIL("latent_flash: %lld floats of scratch are too few for %d shares of the keys", scratch_floats, n_chunks);
+    }
+    const dim3 grid = decode ? dim3((H + LF_ROWS - 1) / LF_ROWS, n_seqs, n_chunks) : dim3(H, n_q_tiles);
     if (grid.y > 65535) SP_FAIL("latent_flash: %u rows of blocks are beyond this kernel's grid", grid.y);
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_seqs * H * n_chunks * rank : nullptr;
     LfArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pool, page_table, seq_row, max_pages,
-             seq_start, positions, n_seqs, sink, H, window, scale * LOG2E, decode ? 1 : 0, sp_range_host};
+             seq_start, positions, n_seqs, sink, H, window, scale * LOG2E, decode ? 1 : 0, sp_range_host,
+             n_chunks, chunk_tiles, part_o, part_ml};
     int rc = 1;
     switch (rank) {
         case 128: rc = launch_latent_flash<128>(grid, stream, a); break;
@@ -436,5 +532,9 @@ SP_API int sp_latent_flash(const void* q, void* out, const void* pool, const int
     }
     if (rc) return 1;
     SP_CHECK_LAUNCH("latent_flash");
+    if (n_chunks > 1) {
+        latent_combine_kernel<<<n_seqs * H, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, seq_start, sink, H, rank, n_chunks);
+        SP_CHECK_LAUNCH("latent_combine");
+    }
     return 0;
 }

@@ -1261,10 +1261,12 @@ def latent_flash_supported(rank: int, page_size: int) -> bool:
     return bool(load("latent").sp_latent_flash_supported(int(rank), int(page_size)))
 
 
-def latent_flash(qc, pool, out, meta, step, H, rank, window, scale, sink=None):
+def latent_flash(qc, pool, out, meta, step, H, rank, window, scale, sink=None, max_len=None):
     """Attention over cached latents on the tensor cores (bfloat16): ``qc`` [T, H·rank] are the queries in the latent's
     space, ``pool`` [pages, 1, 64, rank] the cached rows (key and value at once), ``out`` [T, H·rank] the weighted sums
-    of rows. Window, sink and scale as for the other attention kernels."""
+    of rows. Window, sink and scale as for the other attention kernels. ``max_len``: no sequence of a decode step is
+    longer (the step's longest, or its bucket when the launch is captured in a graph); with it the step's keys are
+    shared out over several blocks per sequence."""
     lib = load("latent")
     _need_contig(qc, out, pool)
     if qc.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -1273,8 +1275,17 @@ def latent_flash(qc, pool, out, meta, step, H, rank, window, scale, sink=None):
     _declare_bounds("latent", lib, _pool_pages(meta, pool), _table_rows(meta, pt), qc.device)
     decode = bool(step.all_single)
     tiles = 0 if decode else query_tiles(step.host["new_counts"], int(lib.sp_latent_flash_rows()))
+    scratch, need = None, 0
+    if decode and max_len:
+        lib.sp_latent_flash_scratch_floats.restype = c_longlong
+        need = int(lib.sp_latent_flash_scratch_floats(int(step.n_seqs), int(H), int(rank), int(window or 0), int(max_len)))
+        if need:
+            scratch = torch.empty(need, dtype=torch.float32, device=qc.device)
     _check("latent", lib.sp_latent_flash(
         c_void_p(_ptr(qc)), c_void_p(_ptr(out)), c_void_p(_ptr(pool)), c_void_p(_ptr(step.seq_start)),
         c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
         int(step.n_seqs), int(tiles), int(decode), int(H), int(rank), int(window or 0), c_float(scale), _sink_ptr(sink, H),
-        c_void_p(_stream())))
+        int(max_len or 0), c_void_p(_ptr(scratch)), c_longlong(need), c_void_p(_stream())))
+    if need:
+        global launches
+        launches += 1        # two kernels: the shares and their combination

@@ -29,7 +29,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib as K
-from .attention import attend_paged
+from .attention import attend_paged, length_bucket
 from .base import KVCacheRequest, Mixer, WeightSpec
 from .linear import Linear
 from .registry import register_part
@@ -142,6 +142,8 @@ class LatentAttention(Mixer):
         H, r = self.num_heads, self.kv_rank
         if qc.dtype == torch.bfloat16 and cache.k_pool.dtype == torch.bfloat16 and K.latent_flash_supported(r, cache.page_size):
             mix = torch.empty_like(qc)
-            K.latent_flash(qc, cache.k_pool, mix, cache, step, H, r, self.window, self.scale, self.sink)
+            # the keys of a decode step are shared out for the length's bucket, as the grouped-query kernel's are
+            max_len = length_bucket(step.max_len, cache.page_size) if step.all_single else None
+            K.latent_flash(qc, cache.k_pool, mix, cache, step, H, r, self.window, self.scale, self.sink, max_len=max_len)
             return mix
         return attend_paged(qc, step, cache, H, 1, r, self.window, self.scale, self.sink, self.counters)

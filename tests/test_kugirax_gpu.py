@@ -314,20 +314,22 @@ def test_attention_over_cached_latents_with_a_window_and_a_sink(kind, H, r, wind
     sink_d = sink.to(DEV)
     counters = torch.zeros(4096, dtype=torch.int32, device=DEV)
 
-    def call(rows, step, view):
+    def call(rows, step, view, split=True):
         if kind == "latent":
             assert K.latent_flash_supported(r, PAGE)
             out = torch.empty_like(rows)
-            K.latent_flash(rows, view.k_pool, out, view, step, H, r, window, scale, sink_d)
+            # with the step's longest length a decode step's keys are shared out over several blocks per sequence
+            K.latent_flash(rows, view.k_pool, out, view, step, H, r, window, scale, sink_d,
+                           max_len=step.max_len if step.all_single and split else None)
             return out
         return attend_paged(rows, step, view, H, 1, r, window, scale, sink_d, counters)
 
     tol = 3e-6 if dtype == torch.float32 else 1.2e-2
-    for cuts in LAT_CUTS:
+    for cuts, split in zip(LAT_CUTS + LAT_CUTS[2:], (True, True, True, False)):
         world = Paged(LAT_PAGES, 12, 1, r, dtype)
-        got = _run_attention(world, q, c, _fix_cuts(cuts), call)
+        got = _run_attention(world, q, c, _fix_cuts(cuts), lambda *a: call(*a, split=split))
         for b in range(3):
-            assert worst(got[b], refs[b]) <= tol, (cuts[b][:4], b)
+            assert worst(got[b], refs[b]) <= tol, (cuts[b][:4], b, split)
     # the sink matters here: without it the result is far away
     no_sink = P.sink_softmax_mix(q[0].double(), c[0].double().expand(-1, H, -1), c[0].double().expand(-1, H, -1), scale,
                                  window, torch.full((H,), -1e30, dtype=torch.float64)).reshape(LAT_LENGTHS[0], -1)
@@ -544,6 +546,34 @@ def test_every_cut_agrees_with_plain(models, name, dtype, tmp_path):
         compare(results[cut], ref, TOL[dtype], f"{name}/{dtype}/{cut}", allow)
     for cut in ("tail", "ragged", "ragged_pairs"):
         compare(results[cut], results["whole"], TOL[dtype], f"{name}/{dtype}: {cut} against whole", allow)
+
+
+def test_a_long_prompt_takes_the_grouped_expert_products_and_the_multiplied_out_maps(tmp_path):
+    """A width and expert sizes that the tcgen05 tile kernel takes: a prompt of 300 tokens (600 and 900 pairs) runs its
+    SwiGLU experts as grouped products and the latent attention's per-head maps multiplied out; the decode steps behind
+    it take the small tiles and the small products; the 32-bit mode FFMA kernels. All agree with plain."""
+    from spissa_b200.csrc import lib as K
+    cfg = model(128, 180, [lat(latent_mixer(4, 32, 16, 64, 128, 100), moe(8, 2, 64, 1.5, shared=64)),
+                           att(conv_mixer(2, 1, 64, conv=3, rot=32), moe(4, 3, 128, 1.0)),
+                           lat(latent_mixer(2, 16, 48, 32, 128, 140, kv_from=0), dense(192))], cap=10.0)
+    pcfg, w = make(cfg, tmp_path, seed=41, std=0.07, norm_std=0.1)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    toks = tiny.random_prompt(180, 330, 8)
+    ref = logits_of(m, toks)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(str(tmp_path), dtype=dtype, max_tokens=64 * 7, max_seqs=1)
+        s = eng.acquire()
+        rows = [eng.step([(s, toks[:300], list(range(300)))]).cpu()]
+        rows += [eng.step([(s, [t], [0])]).cpu() for t in toks[300:]]
+        eng.release(s)
+        got = {("p", i): r for i, r in enumerate(torch.cat(rows))}
+        compare(got, {("p", i): r for i, r in enumerate(ref)}, TOL[dtype], dtype, 0.0 if dtype == "float32" else CLOSE_CALLS)
+        if dtype == "bfloat16":
+            assert eng.model.layers[0].ffn.glu_block == 64 and eng.model.layers[1].ffn.glu_block == 128
+            assert eng.model.layers[0].mixer.q_fold is not None and eng.model.layers[2].mixer.o_fold.weight.shape == (128, 2 * 128)
+        else:
+            assert eng.model.layers[0].mixer.q_fold is None
+    assert "tc_gemm" in K.loaded_libraries()
 
 
 @pytest.mark.parametrize("name", ["a", "c"])
