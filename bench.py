@@ -893,7 +893,8 @@ def kernel_case(name: str, reps: int) -> int:
             uks = [rnd(LH * d, r) for _ in range(n_w)]
             a = rnd(rows, LH * d)
             out = torch.empty(rows, LH * r, dtype=bf, device=dev)
-            run = lambda i: K.headwise_product(a, uks[i % n_w], out, LH, d, r, w_rows_are_k=True)
+            # a decode step streams the stack stored with the outputs as rows, a warp per row
+            run = lambda i: K.headwise_product(a, uks[i % n_w], out, LH, d, r, w_rows_are_k=B == 1)
             if B > 1:
                 bytes_ = LH * d * r * 2.0
             else:

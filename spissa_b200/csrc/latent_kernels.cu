@@ -131,10 +131,65 @@ headwise_product_kernel(const TA* __restrict__ a, const TW* __restrict__ w, TO* 
     }
 }
 
+// The same for a few tokens (a decode step), where the weights' bytes are all there is to do: a warp per output
+// row n of W_h stored [n][k], its lanes striding over k in pairs of bfloat16, the tokens' inputs of this head waiting
+// in shared memory as 32-bit; a lane adds its k in ascending order, the lanes' sums meet by shuffles. HS_ROWS output rows
+// per block keep every SM busy on a stack of a megabyte.
+#define HS_TMAX 16
+#define HS_ROWS 32
+template <typename TA, typename TO>
+__global__ void __launch_bounds__(256)
+headwise_small_kernel(const TA* __restrict__ a, const __nv_bfloat16* __restrict__ w, TO* __restrict__ out, int T, int H, int K, int N) {
+    extern __shared__ float hs_a[];                           // [T][K]
+    const int h = blockIdx.x, n0 = blockIdx.y * HS_ROWS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = threadIdx.x; e < T * K; e += 256) {
+        const int t = e / K, k = e % K;
+        hs_a[e] = sp_ld(a, ((size_t)t * H + h) * K + k);
+    }
+    __syncthreads();
+    const __nv_bfloat16* wh = w + (size_t)h * N * K;
+    for (int n = n0 + warp; n < min(N, n0 + HS_ROWS); n += 8) {
+        const __nv_bfloat162* row = (const __nv_bfloat162*)(wh + (size_t)n * K);
+        float acc[HS_TMAX];
+#pragma unroll
+        for (int t = 0; t < HS_TMAX; ++t) acc[t] = 0.0f;
+#pragma unroll 4
+        for (int k2 = lane; k2 < K / 2; k2 += 32) {
+            const float2 wv = __bfloat1622float2(row[k2]);
+#pragma unroll
+            for (int t = 0; t < HS_TMAX; ++t)
+                if (t < T) {
+                    const float2 av = *(const float2*)(hs_a + t * K + 2 * k2);
+                    acc[t] = fmaf(av.y, wv.y, fmaf(av.x, wv.x, acc[t]));
+                }
+        }
+#pragma unroll
+        for (int t = 0; t < HS_TMAX; ++t)
+            if (t < T) {
+                float v = acc[t];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) sp_st(out, ((size_t)t * H + h) * N + n, v);
+            }
+    }
+}
+
 SP_API int sp_headwise_product(const void* a, int a_dt, const void* w, int w_dt, void* out, int out_dt, int T, int H, int K,
                                int N, int w_rows_are_k, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || K <= 0 || N <= 0) SP_FAIL("headwise_product: sizes %d x %d x %d", H, K, N);
+    if (T <= HS_TMAX && !w_rows_are_k && w_dt == SP_DT_BF16 && K % 2 == 0 && (size_t)T * K * 4 <= 48 * 1024 && H <= 65535 &&
+        (a_dt == SP_DT_BF16 || a_dt == SP_DT_F32) && a_dt == out_dt && ((uintptr_t)w & 3) == 0) {
+        const dim3 grid(H, (N + HS_ROWS - 1) / HS_ROWS);
+        const size_t smem = (size_t)T * K * 4;
+        if (a_dt == SP_DT_BF16)
+            headwise_small_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, T, H, K, N);
+        else
+            headwise_small_kernel<float, float><<<grid, 256, smem, stream>>>((const float*)a, (const __nv_bfloat16*)w, (float*)out, T, H, K, N);
+        SP_CHECK_LAUNCH("headwise_small");
+        return 0;
+    }
     const int tt = T <= 16 ? 8 : 32;
     const dim3 grid((T + tt - 1) / tt, H, (N + HW_TN - 1) / HW_TN);
     if (grid.y > 65535 || grid.z > 65535) SP_FAIL("headwise_product: %d heads or %d outputs are too many for one launch", H, N);

@@ -1245,6 +1245,9 @@ def latent_norm_store(proj, q_rank, rank, wq, wc, eps, cq_out, pool, meta):
         pt.shape[1], meta.page_size, proj.shape[0], int(q_rank), int(rank), c_float(eps), c_void_p(_stream())))
 
 
+HEADWISE_SMALL_TOKENS = 16      # up to this many tokens a stack stored [H·N, K] in bfloat16 is streamed row by row, a warp per row
+
+
 def headwise_product(a, w, out, H, K_, N, w_rows_are_k):
     """out[t, h, :] = a[t, h, :] · W_h with ``a`` [T, H·K], ``out`` [T, H·N] and ``w`` the heads' matrices one after
     another: [H·K, N] (``w_rows_are_k``) or [H·N, K]."""

@@ -90,6 +90,9 @@ class LatentAttention(Mixer):
         self.uk = tensors[n["uk"]].contiguous()            # [H·dim, rank]: head h's rows are U_k,h, a matrix [dim, rank]
         self.uv = tensors[n["uv"]].contiguous()            # [H·vdim, rank]
         self.o = Linear(tensors[n["o"]])
+        # for steps of a few tokens: U_k,h with the latent's entries as its rows, so that both small products stream
+        # rows of a matrix stored [out, in]
+        self.uk_t = self.uk.view(self.num_heads, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
         self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None     # a score: 32-bit
         self.q_fold = self.o_fold = None
         if rt.act_dtype == torch.bfloat16 and all(w.dtype == torch.bfloat16 for w in (self.uk, self.uv, self.uq.weight, self.o.weight)):
@@ -122,7 +125,10 @@ class LatentAttention(Mixer):
                 q = self.uq(cq)
             with phase("query_into_latent_space_ms"):
                 qc = torch.empty(T, H * r, dtype=act, device=dev)
-                K.headwise_product(q, self.uk, qc, H, d, r, w_rows_are_k=True)            # U_k,hᵀ q_h
+                if T <= K.HEADWISE_SMALL_TOKENS:
+                    K.headwise_product(q, self.uk_t, qc, H, d, r, w_rows_are_k=False)     # U_k,hᵀ q_h
+                else:
+                    K.headwise_product(q, self.uk, qc, H, d, r, w_rows_are_k=True)
         with phase("latent_attention_ms"):
             mix = self.attend(qc, step, cache)
         if folded:
