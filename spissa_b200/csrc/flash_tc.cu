@@ -20,8 +20,10 @@
 // Tensor memory: S0 64 columns, S1 64, O 64 of 256 allocated: two CTAs per SM, so that one CTA's softmax runs
 // under the other's products. Heavy tiles (late queries, many keys) are launched first. Every mbarrier wait is
 // bounded; a wait that runs out records a code in ``status`` and every role falls through to the common exit,
-// where tensor memory is freed. No load uses cluster multicast. Built for head size 64 without a window; the
-// host refuses anything else (the mma.sync kernel serves those).
+// where tensor memory is freed. No load uses cluster multicast. Built for head sizes 64 and 128; the host refuses
+// anything else (the mma.sync kernel serves those). A window bounds the walk from below and masks the keys before a
+// row's window in the blocks at that edge. Keys and values come from the paged cache, or (``rows_mode``) from rows
+// [tokens, kv heads x head size] of the step's own tokens when every sequence of the step starts at its position 0.
 #include "tcgen05.cuh"
 
 SP_API const char* sp_flash_tc_last_error() { return sp_error_text; }
@@ -62,7 +64,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int* __restrict__ seq_start, const int* __restrict__ positions,
                         const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
                         int n_seqs, int nh, int nkv, float scale_log2, int* status, SpRange rg,
-                        const float* __restrict__ sink) {
+                        const float* __restrict__ sink, int window, int rows_mode) {
     static_assert(HD == 64 || HD == 128, "scores 2 x 64 columns and the output HD columns of 256 in tensor memory");
     using L = Smem<HD>;
     constexpr int KV_STAGES = kv_stages<HD>();
@@ -93,8 +95,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int pos0 = live ? positions[t0] : 0;
     const int h = blockIdx.x;
     const int g = h / (nh / nkv);
-    const int n_blocks = live ? (pos0 + n_rows - 1) / KB + 1 : 0;
-    const int* pt = page_table + (size_t)(live ? sp_checked_row(seq_row[b], rg) : 0) * max_pages;
+    // Blocks of keys j_lo .. j_end - 1: up to the tile's last row, and with a window from the block that holds the first
+    // key its FIRST row sees (earlier pages may have gone back to the pool). ``it`` counts the blocks a CTA walks: ring
+    // stages, buffer parities and barrier phases go by it, pages and key positions by j = j_lo + it.
+    const int j_end = live ? (pos0 + n_rows - 1) / KB + 1 : 0;
+    const int j_lo = (live && window > 0 && pos0 - window + 1 > 0) ? (pos0 - window + 1) / KB : 0;
+    const int n_blocks = j_end - j_lo;
+    // rows_mode: keys and values are not in pages but rows [tokens, kv heads x HD] of this step's own tokens, every
+    // sequence from its position 0: key k of the sequence is row first + k
+    const int* pt = rows_mode ? nullptr : page_table + (size_t)(live ? sp_checked_row(seq_row[b], rg) : 0) * max_pages;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bar_q), 1);
@@ -137,11 +146,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!mbar_wait(smem_u32(&bar_kv_empty[s]), phase ^ 1u, status, 111)) break;
                 const uint32_t k_dst = kv_smem + s * L::STAGE_BYTES, v_dst = k_dst + L::K_BYTES;
                 mbar_expect_tx(smem_u32(&bar_kv_full[s]), L::STAGE_BYTES);
-                const int r0 = (sp_checked_page(pt[sp_checked_entry(j, max_pages, rg)], rg) * nkv + g) * PAGE;
+                // rows past the tensor's end arrive as zeros, rows of the next sequence are keys after every query here
+                const int r0 = rows_mode ? first + (j_lo + j) * KB
+                                         : (sp_checked_page(pt[sp_checked_entry(j_lo + j, max_pages, rg)], rg) * nkv + g) * PAGE;
+                const int c0 = rows_mode ? g * HD : 0;
 #pragma unroll
                 for (int c = 0; c < L::BOXES; ++c) {
-                    tma_load_2d(k_dst + c * L::KV_BOX, &map_k, c * 64, r0, smem_u32(&bar_kv_full[s]));
-                    tma_load_2d(v_dst + c * L::KV_BOX, &map_v, c * 64, r0, smem_u32(&bar_kv_full[s]));
+                    tma_load_2d(k_dst + c * L::KV_BOX, &map_k, c0 + c * 64, r0, smem_u32(&bar_kv_full[s]));
+                    tma_load_2d(v_dst + c * L::KV_BOX, &map_v, c0 + c * 64, r0, smem_u32(&bar_kv_full[s]));
                 }
             }
         }
@@ -205,11 +217,17 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tc_ld_32x32(s_addr, r);
             tc_ld_32x32(s_addr + 32, r + 32);
             tc_ld_wait();
-            const int key0 = j * KB;
+            const int key0 = (j_lo + j) * KB;
             if (key0 + KB - 1 > pos0) {                           // some row of the tile cannot see some key of the block
 #pragma unroll
                 for (int i = 0; i < KB; ++i)
                     if (key0 + i > qpos) r[i] = 0xff800000u;      // -inf
+            }
+            if (window > 0 && key0 <= pos0 + QT - 1 - window) {   // the block begins before the last row's window
+                const int lo = qpos - window + 1;                 // a row all of whose keys so far are masked keeps m = -inf
+#pragma unroll
+                for (int i = 0; i < KB; ++i)
+                    if (key0 + i < lo) r[i] = 0xff800000u;
             }
             // four chains each for the maximum and the sum: one chain of 64 dependent operations would cost more
             // than the exponentials
@@ -339,11 +357,33 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long l
 SP_API int sp_flash_tc_query_tile() { return QT; }
 
 SP_API int sp_flash_tc_supported(int hd, int nh, int nkv, int page_size, int window) {
-    return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && page_size == PAGE && window <= 0;
+    (void)window;                                                // any window, or none
+    return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && page_size == PAGE;
 }
 
+namespace {
+
+template <int HD>
+int launch_flash_tc(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out,
+                    const int* seq_start, const int* positions, const int* seq_row, const int* page_table, int max_pages,
+                    int n_seqs, int nh, int nkv, float scale, int* status, const float* sink, int window, int rows_mode) {
+    static SpPerDevice configured;
+    if (!configured.done()) {
+        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<HD>::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<HD>::TOTAL, cudaGetErrorString(e));
+        configured.mark();
+    }
+    SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<HD>, grid, dim3(192), (size_t)Smem<HD>::TOTAL, stream,
+        mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
+        scale * LOG2E, status, sp_range_host, sink, window, rows_mode));
+    SP_CHECK_LAUNCH("flash_prefill_tc");
+    return 0;
+}
+
+}  // namespace
+
 // q, out: [T, nh*hd] bfloat16; pools: [n_pages, nkv, 64, hd] bfloat16; n_q_tiles = sum over sequences of
-// ceil(new tokens / 128).
+// ceil(new tokens / 128). ``window`` w > 0: a query at position i sees the keys i - w < j <= i.
 // ``sink`` (float32 per query head, or null): a score that joins every row's denominator once, with no key and no value
 SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
                                     int T, const int* seq_start, const int* positions, const int* seq_row,
@@ -352,7 +392,7 @@ SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool,
                                     cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
     if (!sp_flash_tc_supported(hd, nh, nkv, page_size, window))
-        SP_FAIL("flash_tc: built for head sizes 64 and 128, pages of 64 and no window (got head %d, page %d, window %d)", hd, page_size, window);
+        SP_FAIL("flash_tc: built for head sizes 64 and 128 and pages of 64 (got head %d, page %d)", hd, page_size);
     if (((uintptr_t)q & 15) || ((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15) || ((uintptr_t)out & 15))
         SP_FAIL("flash_tc: operands must start on a 16-byte boundary");
     CUtensorMap mq, mk, mv;
@@ -361,28 +401,35 @@ SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool,
     if (make_map(&mv, vpool, n_pages * nkv * PAGE, hd, hd, PAGE)) return 1;
     if (n_q_tiles > 65535) SP_FAIL("flash_tc: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
-    static SpPerDevice configured[2];
-    if (hd == 64) {
-        if (!configured[0].done()) {
-            cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL);
-            if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<64>::TOTAL, cudaGetErrorString(e));
-            configured[0].mark();
-        }
-        SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<64>, grid, dim3(192), (size_t)Smem<64>::TOTAL, stream,
-            mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status, sp_range_host, sink));
-    } else {
-        if (!configured[1].done()) {
-            cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL);
-            if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<128>::TOTAL, cudaGetErrorString(e));
-            configured[1].mark();
-        }
-        SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<128>, grid, dim3(192), (size_t)Smem<128>::TOTAL, stream,
-            mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status, sp_range_host, sink));
-    }
-    SP_CHECK_LAUNCH("flash_prefill_tc");
-    return 0;
+    const int w = window > 0 ? window : 0;
+    return hd == 64 ? launch_flash_tc<64>(grid, stream, mq, mk, mv, out, seq_start, positions, seq_row, page_table, max_pages,
+                                          n_seqs, nh, nkv, scale, status, sink, w, 0)
+                    : launch_flash_tc<128>(grid, stream, mq, mk, mv, out, seq_start, positions, seq_row, page_table, max_pages,
+                                           n_seqs, nh, nkv, scale, status, sink, w, 0);
+}
+
+// The same over keys and values that are not in a cache: ``k`` and ``v`` [T, nkv*hd] bfloat16 hold the step's own
+// tokens, and every sequence of the step starts at its position 0 (the caller's promise: ``positions`` of a
+// sequence's first token is 0), so that key j of sequence b is row seq_start[b] + j.
+SP_API int sp_flash_prefill_tc_rows(const void* q, void* out, const void* k, const void* v, int T, const int* seq_start,
+                                    const int* positions, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
+                                    float scale, int* status, const float* sink, cudaStream_t stream) {
+    if (n_q_tiles <= 0) return 0;
+    if (!sp_flash_tc_supported(hd, nh, nkv, PAGE, window))
+        SP_FAIL("flash_tc: built for head sizes 64 and 128 (got head %d, %d heads over %d)", hd, nh, nkv);
+    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
+        SP_FAIL("flash_tc: operands must start on a 16-byte boundary");
+    CUtensorMap mq, mk, mv;
+    if (make_map(&mq, q, T, nh * hd, (long long)nh * hd, QT)) return 1;
+    if (make_map(&mk, k, T, nkv * hd, (long long)nkv * hd, PAGE)) return 1;
+    if (make_map(&mv, v, T, nkv * hd, (long long)nkv * hd, PAGE)) return 1;
+    if (n_q_tiles > 65535) SP_FAIL("flash_tc: %d query tiles are beyond this kernel's grid", n_q_tiles);
+    dim3 grid(nh, n_q_tiles);
+    const int w = window > 0 ? window : 0;
+    return hd == 64 ? launch_flash_tc<64>(grid, stream, mq, mk, mv, out, seq_start, positions, nullptr, nullptr, 0,
+                                          n_seqs, nh, nkv, scale, status, sink, w, 1)
+                    : launch_flash_tc<128>(grid, stream, mq, mk, mv, out, seq_start, positions, nullptr, nullptr, 0,
+                                           n_seqs, nh, nkv, scale, status, sink, w, 1);
 }
 
 SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,

@@ -25,6 +25,7 @@ struct LnArgs {
     const void* wq; const void* wc; int w_dt;       // norm weights [qr], [rank]
     void* cq; int cq_dt;                            // [T][qr]
     void* pool; int pool_dt;                        // [pages][page_size][rank], or null: the latent part is absent
+    void* rows;                                     // [T][rank] like cq, or null: the same latents token by token
     const int* token_seq; const int* positions; const int* seq_row; const int* page_table; int max_pages, page_size;
     int T, qr, rank;
     float eps;
@@ -54,17 +55,20 @@ __global__ void __launch_bounds__(256) latent_norm_store_kernel(LnArgs a) {
     const int page = a.page_table[(size_t)prow * a.max_pages + pos / a.page_size];
     if (!sp_index_ok(page, a.rg.n_pages, a.rg, 401)) return;
     const size_t base = ((size_t)page * a.page_size + pos % a.page_size) * a.rank;
-    for (int i = threadIdx.x; i < a.rank; i += blockDim.x)
-        sp_st_dt(a.pool, a.pool_dt, base + i, lat[i] * inv_c * sp_ld_dt(a.wc, a.w_dt, i));
+    for (int i = threadIdx.x; i < a.rank; i += blockDim.x) {
+        const float c = lat[i] * inv_c * sp_ld_dt(a.wc, a.w_dt, i);
+        sp_st_dt(a.pool, a.pool_dt, base + i, c);
+        if (a.rows) sp_st_dt(a.rows, a.cq_dt, (size_t)t * a.rank + i, c);
+    }
 }
 
 SP_API int sp_latent_norm_store(const float* proj, int ld, const void* wq, const void* wc, int w_dt, void* cq, int cq_dt,
                                 void* pool, int pool_dt, const int* token_seq, const int* positions, const int* seq_row,
                                 const int* page_table, int max_pages, int page_size, int T, int qr, int rank, float eps,
-                                cudaStream_t stream) {
+                                void* rows, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (qr <= 0 || rank <= 0 || ld < qr + (pool ? rank : 0)) SP_FAIL("latent_norm_store: parts of %d and %d do not fit rows of %d", qr, rank, ld);
-    LnArgs a{proj, ld, wq, wc, w_dt, cq, cq_dt, pool, pool_dt, token_seq, positions, seq_row, page_table, max_pages,
+    LnArgs a{proj, ld, wq, wc, w_dt, cq, cq_dt, pool, pool_dt, rows, token_seq, positions, seq_row, page_table, max_pages,
              page_size, T, qr, rank, eps, sp_range_host};
     latent_norm_store_kernel<<<T, 256, 0, stream>>>(a);
     SP_CHECK_LAUNCH("latent_norm_store");

@@ -686,7 +686,7 @@ def gemv_qkv_rope(x, w, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd):
 
 # ------------------------------------------------------------------ prefill attention on tcgen05
 def flash_tc_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd: int, page_size: int, window) -> bool:
-    """Whether the tcgen05 prefill attention takes this shape (head 64 or 128, pages of 64, no window, bfloat16)."""
+    """Whether the tcgen05 prefill attention takes this shape (head 64 or 128, pages of 64, bfloat16; any window)."""
     return (q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and k_pool.is_contiguous()
             and bool(load("flash_tc").sp_flash_tc_supported(int(hd), int(nh), int(nkv), int(page_size), int(window or 0))))
 
@@ -706,6 +706,25 @@ def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles,
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles),
         nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_ptr(status_word(q.device))), _sink_ptr(sink, nh),
         c_void_p(_stream())))
+
+
+def flash_tc_rows_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
+    """Whether ``flash_prefill_tc_rows`` takes queries, keys and values of this type and shape."""
+    return dtype == torch.bfloat16 and bool(load("flash_tc").sp_flash_tc_supported(int(hd), int(nh), int(nkv), 64, 0))
+
+
+def flash_prefill_tc_rows(q, k, v, out, step, n_q_tiles, nh, nkv, hd, window, scale, sink=None):
+    """The tcgen05 prefill attention over keys and values that lie in no cache: ``k`` and ``v`` [T, nkv·hd] bfloat16
+    are the step's own tokens, and EVERY sequence of the step starts at its position 0 (the caller has checked)."""
+    lib = load("flash_tc")
+    _need_contig(q, out, k, v)
+    T = q.shape[0]
+    if k.shape != (T, nkv * hd) or v.shape != (T, nkv * hd) or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise KernelError("flash_tc: keys and values as rows are bfloat16 [tokens, kv heads x head size]")
+    _check("flash_tc", lib.sp_flash_prefill_tc_rows(
+        c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k)), c_void_p(_ptr(v)), T, c_void_p(_ptr(step.seq_start)),
+        c_void_p(_ptr(step.positions)), int(step.n_seqs), int(n_q_tiles), nh, nkv, hd, int(window or 0), c_float(scale),
+        c_void_p(_ptr(status_word(q.device))), _sink_ptr(sink, nh), c_void_p(_stream())))
 
 
 # ------------------------------------------------------------------ all layers of a decode step in one kernel
@@ -1227,14 +1246,16 @@ def moe_experts(x, ids, weights, w_gate_up, w_down, y, top, limit, slope=1.702, 
 
 
 # ------------------------------------------------------------------ latent: attention through a cached low-rank latent
-def latent_norm_store(proj, q_rank, rank, wq, wc, eps, cq_out, pool, meta):
+def latent_norm_store(proj, q_rank, rank, wq, wc, eps, cq_out, pool, meta, rows_out=None):
     """``proj`` rows (float32) = [q part: ``q_rank`` | latent part: ``rank``]: each part's RMS norm with its weight; the
     q part to ``cq_out`` [T, q_rank], the latent into its page row of ``pool`` ([pages, 1, page_size, rank]; None: the
-    rows carry no latent part)."""
+    rows carry no latent part). ``rows_out`` [T, rank] of ``cq_out``'s type also receives the latents, token by token."""
     lib = load("latent")
     if proj.dtype != torch.float32:
         raise KernelError("latent_norm_store reads 32-bit projections")
-    _need_contig(proj, wq, wc, cq_out)
+    _need_contig(proj, wq, wc, cq_out, rows_out)
+    if rows_out is not None and (pool is None or rows_out.dtype != cq_out.dtype or rows_out.shape != (proj.shape[0], int(rank))):
+        raise KernelError("latent_norm_store: the latents as rows are [tokens, rank] of the q part's type, beside a pool")
     pt = meta.page_table
     if pool is not None:
         _declare_bounds("latent", lib, _pool_pages(meta, pool), _table_rows(meta, pt), proj.device)
@@ -1242,7 +1263,8 @@ def latent_norm_store(proj, q_rank, rank, wq, wc, eps, cq_out, pool, meta):
         c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(wq)), c_void_p(_ptr(wc)), _w_dt(*[w for w in (wq, wc) if w is not None]),
         c_void_p(_ptr(cq_out)), dt_code(cq_out), c_void_p(_ptr(pool)), dt_code(pool) if pool is not None else 0,
         c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)),
-        pt.shape[1], meta.page_size, proj.shape[0], int(q_rank), int(rank), c_float(eps), c_void_p(_stream())))
+        pt.shape[1], meta.page_size, proj.shape[0], int(q_rank), int(rank), c_float(eps), c_void_p(_ptr(rows_out)),
+        c_void_p(_stream())))
 
 
 HEADWISE_SMALL_TOKENS = 16      # up to this many tokens a stack stored [H·N, K] in bfloat16 is streamed row by row, a warp per row

@@ -23,6 +23,13 @@ take the same maps multiplied out once when the weights are bound,
 
 (products in 32-bit, rounded once to bfloat16), so that both are plain matrix products on the tile kernel: more FLOPs
 than the small products, but at the tensor cores' rate instead of a per-head loop.
+
+A third way for prompt steps in which EVERY sequence starts at its position 0 (whole prompts: nothing the step's
+queries see lies in the cache only), with heads the tcgen05 attention kernel takes (key size = value size = 64 or
+128): the step's own latents, kept as rows [tokens, rank] by the kernel that writes them into their pages (a reader
+layer finds its writer's rows in the step's scratch), ARE expanded, K = C U_kᵀ and V = C U_vᵀ as two plain products,
+and the attention runs over them with the window and the sinks: 2·(dim + vdim) FLOPs per visible pair and head instead
+of 4·rank, on the faster kernel. The cache is written all the same; later steps read it.
 """
 from __future__ import annotations
 
@@ -36,6 +43,7 @@ from .registry import register_part
 from ..phases import phase
 
 _UNSET = object()
+EXPANDED_FROM_TOKENS = 256   # prompt steps from position 0 with at least this many tokens expand their own keys and values
 FOLDED_FROM_TOKENS = 64      # steps of more tokens than this take the multiplied-out maps (bfloat16): below, the weights'
 #                              bytes decide, and the small products read a third of them
 
@@ -94,6 +102,7 @@ class LatentAttention(Mixer):
         # rows of a matrix stored [out, in]
         self.uk_t = self.uk.view(self.num_heads, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
         self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None     # a score: 32-bit
+        self.uk_rows, self.uv_rows = Linear(self.uk), Linear(self.uv)                      # K = C U_kᵀ, V = C U_vᵀ
         self.q_fold = self.o_fold = None
         if rt.act_dtype == torch.bfloat16 and all(w.dtype == torch.bfloat16 for w in (self.uk, self.uv, self.uq.weight, self.o.weight)):
             H, d, vd, qr, r = self.num_heads, self.head_dim, self.v_head_dim, self.q_rank, self.kv_rank
@@ -112,10 +121,30 @@ class LatentAttention(Mixer):
             raise ValueError(f"{self.prefix}: a layer without a latent projection cannot be the writer of a cache")
         with phase("latent_projection_ms"):
             proj = (self.down if writes else self.down_q)(x, out_dtype=torch.float32)     # the norms read unrounded products
+        rows_key = ("latent_rows", cache.k_pool.data_ptr())
+        expand = (act == torch.bfloat16 and T >= EXPANDED_FROM_TOKENS and d == vd and self.uk.dtype == torch.bfloat16
+                  and step.host.get("seq_len") is not None and step.host["seq_len"] == step.host["new_counts"]
+                  and (writes or rows_key in step.scratch) and K.flash_tc_rows_supported(act, H, H, d))
         with phase("latent_norm+append_ms"):
             cq = torch.empty(T, qr, dtype=act, device=dev)
+            rows = torch.empty(T, r, dtype=act, device=dev) if expand and writes else None
             K.latent_norm_store(proj, qr, r, self.wq_norm, self.wc_norm if writes else None, self.eps, cq,
-                                cache.k_pool if writes else None, cache)
+                                cache.k_pool if writes else None, cache, rows_out=rows)
+            if rows is not None:
+                step.scratch[rows_key] = rows          # the layers that read this cache expand the same rows
+        if expand:
+            rows = step.scratch[rows_key]
+            with phase("q_projection_ms"):
+                q = self.uq(cq)
+            with phase("key_value_expansion_ms"):
+                k, v = self.uk_rows(rows), self.uv_rows(rows)
+            with phase("latent_attention_ms"):
+                ctx = torch.empty_like(q)
+                tiles = K.query_tiles(step.host["new_counts"], K.flash_tc_query_tile())
+                K.flash_prefill_tc_rows(q, k, v, ctx, step, tiles, H, H, d, self.window, self.scale, self.sink)
+            with phase("o_projection+attention_residual_ms"):
+                self.o(ctx, out=residual, accumulate=True)
+            return
         folded = self.q_fold is not None and T > FOLDED_FROM_TOKENS
         if folded:
             with phase("q_projection_ms"):

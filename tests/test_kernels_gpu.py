@@ -651,6 +651,24 @@ def test_flash_prefill_tc(K, nh, nkv, hd):
     attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [1, 1, 1], [0, 63, 300], None, nh + 1, 6e-3)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window", [1, 5, 63, 64, 65, 128, 129, 200, 1000])
+def test_flash_prefill_tc_window(K, hd, window):
+    """A window bounds the walk over the key blocks from below and masks the blocks at its edge: windows below, at and
+    above a block and a query tile, prompts from position 0 and portions behind cached tokens."""
+    fn = flash_tc_fn(K)
+    attention_case(K, fn, 4, 2, hd, torch.bfloat16, [300, 64, 128, 129], [0, 0, 100, 27], window, window, 6e-3)
+    attention_case(K, fn, 3, 1, hd, torch.bfloat16, [130, 1, 257], [250, 300, 64], window, window + 1, 6e-3)
+
+
+@pytest.mark.parametrize("needle,window", [(200, 100), (200, 99), (63, 237), (63, 236), (236, 64), (235, 64), (299, 1), (298, 1)])
+def test_flash_prefill_tc_window_edge(K, needle, window):
+    # a query at 299 and a key that dominates wherever it is seen: seen exactly when 299 - key < window
+    out, v = needle_case(K, flash_tc_fn(K), torch.bfloat16, 300, needle, window=window)
+    hit = all(torch.allclose(out[h], v[needle, h // 2], atol=2e-2) for h in range(4))
+    assert hit == (299 - needle < window)
+
+
 @pytest.mark.parametrize("length,needle", [(700, 3), (700, 640), (129, 64), (64, 63), (1000, 0), (65, 64), (257, 128)])
 def test_flash_prefill_tc_finds_a_far_key(K, length, needle):
     out, v = needle_case(K, flash_tc_fn(K), torch.bfloat16, length, needle)

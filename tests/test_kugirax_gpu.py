@@ -337,7 +337,8 @@ def test_attention_over_cached_latents_with_a_window_and_a_sink(kind, H, r, wind
 
 
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, None), (8, 1, 96, None), (6, 3, 16, 70), (2, 2, 128, None),
-                                              (3, 1, 10, None), (4, 4, 32, 9)])
+                                              (3, 1, 10, None), (4, 4, 32, 9), (4, 2, 64, 70), (2, 1, 128, 128),
+                                              (4, 4, 64, 200), (2, 2, 128, 33)])
 def test_sinks_in_the_grouped_query_kernels(nh, nkv, hd, window):
     """The same sink on every kernel that serves a grouped-query attention: the generic one (32-bit, any size), the
     mma.sync prompt and split-key decode kernels and, for prompts of 256 tokens and more, the tcgen05 one. A sink of 0
@@ -358,7 +359,7 @@ def test_sinks_in_the_grouped_query_kernels(nh, nkv, hd, window):
             sd = sink.to(DEV)
             call = lambda rows, step, view: attend_paged(rows, step, view, nh, nkv, hd, window, scale, sd, counters)
             for cuts in ([[300], [70], [131]], [[280] + [1] * 20, [50] + [1] * 20, [111] + [1] * 20],
-                         [[2, 62, 64, 172], [3, 1, 66, 0], [64, 64, 2, 1]]):
+                         [[2, 62, 64, 172], [3, 1, 66, 0], [64, 64, 2, 1]], [[20, 280], [6, 64], [3, 128]]):
                 world = Paged(pages, 14, nkv, hd, dtype, with_values=True)
                 got = _run_attention(world, q, k, cuts, call, v=v)
                 for b in range(3):
@@ -367,6 +368,50 @@ def test_sinks_in_the_grouped_query_kernels(nh, nkv, hd, window):
             none = P.sink_softmax_mix(q[1].double(), k[1].double().repeat_interleave(rep, 1), v[1].double().repeat_interleave(rep, 1),
                                       scale, window, torch.full((nh,), -1e30, dtype=torch.float64)).reshape(70, -1)
             assert worst(none, refs[1]) > 0.05
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, None), (4, 4, 64, 70), (2, 1, 128, 128), (3, 3, 64, 1),
+                                              (4, 4, 128, 200), (2, 2, 64, 64), (4, 1, 128, 65)])
+def test_keys_and_values_as_rows_of_the_steps_own_tokens(nh, nkv, hd, window):
+    """The tcgen05 prompt kernel over keys and values that lie in no cache (a latent attention expands a whole prompt's
+    own latents): ragged sequences that all start at 0, windows below, at and above a block and a tile, sinks. One key
+    of the first sequence is made to stand out, so that a window's edge that is one token off shows."""
+    from spissa_b200.csrc import lib as K
+    lengths = [300, 64, 129, 5, 410]
+    g = torch.Generator().manual_seed(nh * hd + (window or 0))
+    q = [torch.randn(n, nh, hd, generator=g).bfloat16() for n in lengths]
+    k = [torch.randn(n, nkv, hd, generator=g).bfloat16() for n in lengths]
+    v = [torch.randn(n, nkv, hd, generator=g).bfloat16() for n in lengths]
+    scale, rep = 1.0 / math.sqrt(hd), nh // nkv
+    q[0][:, :, 0] = 6.0
+    k[0][150] = 0.0
+    k[0][150, :, 0] = 6.0 * math.sqrt(hd) / 8.0              # a score of 4.5 where the others are about 1
+    sink = torch.linspace(-2.0, 3.0, nh)
+    refs = [P.sink_softmax_mix(qb.double(), kb.double().repeat_interleave(rep, 1), vb.double().repeat_interleave(rep, 1),
+                               scale, window, sink.double()).reshape(qb.shape[0], -1) for qb, kb, vb in zip(q, k, v)]
+    starts = [0]
+    for n in lengths:
+        starts.append(starts[-1] + n)
+    step = SimpleNamespace(seq_start=i32(starts), positions=i32([p for n in lengths for p in range(n)]), n_seqs=len(lengths))
+    flat = lambda xs, h: torch.cat(xs).reshape(-1, h * hd).to(DEV).contiguous()
+    qd, kd, vd = flat(q, nh), flat(k, nkv), flat(v, nkv)
+    assert K.flash_tc_rows_supported(torch.bfloat16, nh, nkv, hd)
+    for sk, want in ((sink.to(DEV), refs), (None, None)):
+        out = torch.full_like(qd, float("nan"))
+        K.flash_prefill_tc_rows(qd, kd, vd, out, step, K.query_tiles(lengths, K.flash_tc_query_tile()), nh, nkv, hd, window, scale, sk)
+        K.check_status(DEV)
+        if want is None:
+            want = [P.sink_softmax_mix(qb.double(), kb.double().repeat_interleave(rep, 1), vb.double().repeat_interleave(rep, 1),
+                                       scale, window, torch.full((nh,), -1e30, dtype=torch.float64)).reshape(qb.shape[0], -1)
+                    for qb, kb, vb in zip(q, k, v)]
+        for b, n in enumerate(lengths):
+            assert worst(out[starts[b]:starts[b] + n], want[b]) <= 1.2e-2, (b, sk is None)
+    if window and 150 + window < 300:
+        # the edge shows: with the standing-out key one place further the rows just past its window differ by far more
+        rows = slice(150 + window - 1, 150 + window + 1)
+        wide = P.sink_softmax_mix(q[0].double(), k[0].double().repeat_interleave(rep, 1), v[0].double().repeat_interleave(rep, 1),
+                                  scale, window + 1, sink.double()).reshape(300, -1)
+        assert worst(wide[rows], refs[0][rows]) > 0.05
 
 
 @pytest.mark.parametrize("nh,nkv,d,taps,rd,dtype", [(4, 2, 16, 4, 8, torch.float32), (3, 1, 10, 5, 6, torch.float32),
@@ -574,6 +619,48 @@ def test_a_long_prompt_takes_the_grouped_expert_products_and_the_multiplied_out_
         else:
             assert eng.model.layers[0].mixer.q_fold is None
     assert "tc_gemm" in K.loaded_libraries()
+
+
+def test_whole_prompts_expand_their_own_latents(tmp_path, monkeypatch):
+    """Latent heads whose key and value sizes the tcgen05 prompt kernel takes: a step in which every prompt starts at
+    its first token expands that step's latents into keys and values (the writer's rows serve its reader too, each
+    with its own window, narrower and wider than a block and a tile); a portion behind cached tokens and the decode
+    steps attend over the cached rows. All agree with plain, and with each other."""
+    from spissa_b200.csrc import lib as K
+    cfg = model(128, 150, [lat(latent_mixer(2, 64, 64, 48, 96, 100), dense(64)),
+                           att(conv_mixer(2, 1, 32, conv=2, rot=16), None),
+                           lat(latent_mixer(1, 128, 128, 32, 96, 270, kv_from=0), moe(4, 2, 64, 1.0)),
+                           lat(latent_mixer(3, 64, 64, 40, 64, 30), None)], cap=15.0)
+    pcfg, w = make(cfg, tmp_path, seed=43, std=0.07, norm_std=0.1)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    reqs = {"p": tiny.random_prompt(150, 336, 5), "r": tiny.random_prompt(150, 296, 6)}
+    ref = {(rid, i): row for rid, toks in reqs.items() for i, row in enumerate(logits_of(m, toks))}
+    calls = []
+    real = K.flash_prefill_tc_rows
+    monkeypatch.setattr(K, "flash_prefill_tc_rows", lambda *a, **kw: (calls.append(a[0].shape[0]), real(*a, **kw))[1])
+    for dtype in ("float32", "bfloat16"):
+        allow = 0.0 if dtype == "float32" else CLOSE_CALLS
+        eng = Engine.from_folder(str(tmp_path), dtype=dtype, max_tokens=64 * 14, max_seqs=2)
+        calls.clear()
+        sp, sr = eng.acquire(), eng.acquire()
+        rows = eng.step([(sp, reqs["p"][:330], list(range(330))), (sr, reqs["r"][:290], list(range(290)))]).cpu()
+        got = {("p", i): rows[i] for i in range(330)}
+        got.update({("r", i): rows[330 + i] for i in range(290)})
+        for i in range(6):
+            rows = eng.step([(sp, [reqs["p"][330 + i]], [0]), (sr, [reqs["r"][290 + i]], [0])]).cpu()
+            got[("p", 330 + i)], got[("r", 290 + i)] = rows[0], rows[1]
+        eng.release(sp), eng.release(sr)
+        assert calls == ([620] * 3 if dtype == "bfloat16" else []), calls
+        compare(got, ref, TOL[dtype], f"{dtype}: two whole prompts", allow)
+        # the same prompt behind 40 cached tokens: nothing is expanded, the cached rows are read
+        calls.clear()
+        s = eng.acquire()
+        eng.step([(s, reqs["p"][:40], [])])
+        rows = eng.step([(s, reqs["p"][40:330], list(range(290)))]).cpu()
+        eng.release(s)
+        assert calls == []
+        compare({("p", 40 + i): rows[i] for i in range(290)}, {k: v for k, v in ref.items() if k[0] == "p" and 40 <= k[1] < 330},
+                TOL[dtype], f"{dtype}: a portion behind cached tokens", allow)
 
 
 @pytest.mark.parametrize("name", ["a", "c"])
