@@ -409,7 +409,7 @@ def design_rooflines(size, row, T, B, peaks, eb) -> dict:
     out["mingru (hbm)"] = dict(ms=dz.get("mingru_ms"), frac=frac(4 * T * W * (3 * 4.0 + eb), bw, dz.get("mingru_ms")))
     out["polynorm (hbm)"] = dict(ms=dz.get("activation_ms"), frac=frac(10 * T * ff * (4.0 + eb), bw, dz.get("activation_ms")))
     out["norm+shift (hbm)"] = dict(ms=dz.get("mixer_norm+shift_ms"), frac=frac(10 * T * W * (4.0 + eb), bw, dz.get("mixer_norm+shift_ms")))
-    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))   # one launch: the first layer's
     return out
 
 
@@ -443,7 +443,7 @@ def gozatar_rooflines(size, goz, row, T, peaks, eb) -> dict:
     norm_ms = (gz.get("attention_norm_ms") or 0) + (gz.get("streams_update+mlp_norm_ms") or 0) + (gz.get("streams_update_ms") or 0)
     # per layer: the streams read once for the first norm, read and written by each of the two updates, y read twice
     out["streams+norm (hbm)"] = dict(ms=norm_ms, frac=frac(L * T * W * (2 * 4.0 + 2 * (4 * 4.0 + 4.0) + 2 * eb), bw, norm_ms))
-    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))   # one launch: the first layer's
     act_ms = gz.get("activation_ms")
     out["activations (hbm)"] = dict(ms=act_ms, frac=frac((2 * T * ff + n_moe * T * 3 * (ff // 4)) * (4.0 + eb) * 1.0, bw, act_ms))
     return out
@@ -467,12 +467,12 @@ def kugirax_rooflines(size, kx, row, T, peaks, eb) -> dict:
                                                       frac=frac(n_att * 4.0 * (T * (T + 1) / 2) * d * h, tf, kz.get("attention_ms")))
     ll_att, ll_runs = ll.get("attention_ms"), row["llama"]["layer_runs"]
     out["llama attention (tensor)"] = dict(ms=ll_att, frac=frac(ll_runs * 4.0 * (T * (T + 1) / 2) * hd * nh, tf, ll_att))
-    # over latents: per (query, visible row) pair and head 2·rank FLOPs for the score and 2·rank for the weighted sum
+    # a whole prompt expands its own latents: per (query, visible key) pair and head 2·dim FLOPs for the score and
+    # 2·vdim for the weighted sum, the least any form does (over the cached rows themselves it is 4·rank)
     out["latent attention (tensor)"] = dict(ms=kz.get("latent_attention_ms"),
-                                            frac=frac(n_lat * 4.0 * pairs * r * lh, tf, kz.get("latent_attention_ms")))
-    # the same attention on expanded keys and values would do 2·dim + 2·vdim per pair: the least any form does
-    out["latent attention, expanded count (tensor)"] = dict(ms=kz.get("latent_attention_ms"),
-                                                            frac=frac(n_lat * 2.0 * pairs * (ld + lvd) * lh, tf, kz.get("latent_attention_ms")))
+                                            frac=frac(n_lat * 2.0 * pairs * (ld + lvd) * lh, tf, kz.get("latent_attention_ms")))
+    out["key and value expansion (tensor)"] = dict(ms=kz.get("key_value_expansion_ms"),
+                                                   frac=frac(n_lat * T * 2.0 * r * lh * (ld + lvd), tf, kz.get("key_value_expansion_ms")))
     hp = (kz.get("query_into_latent_space_ms") or 0) + (kz.get("value_expansion_ms") or 0)
     out["per-head products (tensor)"] = dict(ms=hp, frac=frac(n_lat * T * lh * 2.0 * r * (ld + lvd), tf, hp))
     out["latent norms+append (hbm)"] = dict(ms=kz.get("latent_norm+append_ms"),
@@ -485,7 +485,8 @@ def kugirax_rooflines(size, kx, row, T, peaks, eb) -> dict:
     out["conv+rotary+store (hbm)"] = dict(ms=kz.get("conv+rotary+kv_append_ms"),
                                           frac=frac(n_att * T * (C * 4.0 + (h + 2 * g) * d * eb), bw, kz.get("conv+rotary+kv_append_ms")))
     out["norm (hbm)"] = dict(ms=kz.get("input_norm_ms"), frac=frac(KUGIRAX_LAYERS * T * W * (4.0 + eb), bw, kz.get("input_norm_ms")))
-    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    # Llama's norms ride in the products' prologues but for the first layer's: one launch
+    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
     return out
 
 
@@ -848,7 +849,8 @@ def kernel_case(name: str, reps: int) -> int:
                                    seq_slot=i32([0]), positions=step.positions, token_seq=step.token_seq)
             run = lambda i: K.conv_qk_store(qkvs[i % 4], conv, 4, state, q, kp, vp, meta, step, inv_freq, nh, nkv, d, d, d // 2, 1e-6)
             bytes_ = T * C * (4 + 2.0)
-    elif name in ("latent_flash", "latent_flash_b8", "latent_window_as_gqa", "latent_norm_store", "headwise_b8", "headwise"):
+    elif name in ("latent_flash", "latent_flash_b8", "latent_window_as_gqa", "latent_expanded", "latent_norm_store", "headwise_b8",
+                  "headwise"):
         # the Kugirax latent attention at the 2k size of --design (16 heads over rows of 256, a window of 1,024, sinks)
         LH, r, d, qr, win = 16, 256, 128, 768, 1024
         B = 8 if name.endswith("_b8") else 1
@@ -881,6 +883,14 @@ def kernel_case(name: str, reps: int) -> int:
             q = rnd(rows, LH * d)
             out = torch.empty_like(q)
             run = lambda i: K.flash_prefill(q, kp, vp, out, meta, step.seq_start, 1, T // 64, LH, 4, d, win, d ** -0.5, sink=sink)
+            flops = 4.0 * pairs * d * LH
+        elif name == "latent_expanded":
+            # what a whole prompt runs: the tcgen05 kernel over the prompt's own expanded keys and values, as rows
+            ks, vs = [rnd(rows, LH * d) for _ in range(4)], [rnd(rows, LH * d) for _ in range(4)]
+            q = rnd(rows, LH * d)
+            out = torch.empty_like(q)
+            tiles = K.query_tiles([T], K.flash_tc_query_tile())
+            run = lambda i: K.flash_prefill_tc_rows(q, ks[i % 4], vs[i % 4], out, step, tiles, LH, LH, d, win, d ** -0.5, sink)
             flops = 4.0 * pairs * d * LH
         elif name == "latent_norm_store":
             projs = [torch.randn(T, qr + r, device=dev) for _ in range(4)]

@@ -365,7 +365,8 @@ __global__ void __launch_bounds__(CQV_WARPS * 32) conv_qk_store_vec_kernel(CqArg
     }
     const int off = pos % a.page_size;
     float* st = a.taps > 1 ? a.state + (size_t)slot * n * C : nullptr;
-    for (int hh = warp; hh < nh + (a.v_from_k ? 1 : 2) * nkv; hh += CQV_WARPS) {
+    // a step of few tokens shares a token's heads out over gridDim.y blocks (a head's channels stay with one warp)
+    for (int hh = blockIdx.y * CQV_WARPS + warp; hh < nh + (a.v_from_k ? 1 : 2) * nkv; hh += CQV_WARPS * gridDim.y) {
         const bool is_v = hh >= nh + nkv;
         const int size = is_v ? vd : d;
         const int cb = is_v ? (nh + nkv) * d + (hh - nh - nkv) * vd : hh * d;
@@ -468,7 +469,10 @@ SP_API int sp_conv_qk_store(const float* qkv, int ld, const void* conv, int conv
              eps, v_scale, unit_rms, (all_single && taps > 1) ? 1 : 0, v_from_k ? 1 : 0, sp_range_host};
     const bool wide = d % 4 == 0 && vd % 4 == 0 && (rd / 2) % 4 == 0 && ld % 4 == 0 &&
                       ((((uintptr_t)qkv) | ((uintptr_t)state) | ((uintptr_t)q_out) | ((uintptr_t)kpool) | ((uintptr_t)vpool)) & 15) == 0;
-    if (wide) conv_qk_store_vec_kernel<<<T, CQV_WARPS * 32, 0, stream>>>(a);
+    const int head_rows = nh + (v_from_k ? 1 : 2) * nkv;
+    const int by_heads = (head_rows + CQV_WARPS - 1) / CQV_WARPS, by_sms = 296 / (T < 296 ? T : 296);
+    const int shares = T >= 148 ? 1 : (by_heads < by_sms ? by_heads : by_sms);
+    if (wide) conv_qk_store_vec_kernel<<<dim3(T, shares), CQV_WARPS * 32, 0, stream>>>(a);
     else conv_qk_store_kernel<<<T, CQ_WARPS * 32, 0, stream>>>(a);
     SP_CHECK_LAUNCH("conv_qk_store");
     if (taps > 1 && !all_single) {
