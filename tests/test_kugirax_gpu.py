@@ -336,7 +336,7 @@ def test_attention_over_cached_latents_with_a_window_and_a_sink(kind, H, r, wind
     assert worst(no_sink, refs[0]) > 0.05
 
 
-@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, None), (8, 1, 96, None), (6, 3, 16, 70), (2, 2, 128, None),
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, None), (10, 2, 96, None), (6, 3, 16, 70), (2, 2, 128, None),
                                               (3, 1, 10, None), (4, 4, 32, 9), (4, 2, 64, 70), (2, 1, 128, 128),
                                               (4, 4, 64, 200), (2, 2, 128, 33)])
 def test_sinks_in_the_grouped_query_kernels(nh, nkv, hd, window):
@@ -415,7 +415,7 @@ def test_keys_and_values_as_rows_of_the_steps_own_tokens(nh, nkv, hd, window):
 
 
 @pytest.mark.parametrize("nh,nkv,d,taps,rd,dtype", [(4, 2, 16, 4, 8, torch.float32), (3, 1, 10, 5, 6, torch.float32),
-                                                    (8, 1, 96, 4, 96, torch.bfloat16), (2, 2, 7, 1, 0, torch.float32),
+                                                    (10, 2, 96, 3, 96, torch.bfloat16), (2, 2, 7, 1, 0, torch.float32),
                                                     (6, 3, 16, 2, 16, torch.float32)])
 def test_values_are_the_keys_as_they_leave_the_convolution(nh, nkv, d, taps, rd, dtype):
     """Rows [q | k] only: the convolution over the step's rows and the slot's state, q and k rotated, the values the
@@ -864,7 +864,7 @@ def test_a_reader_of_another_layers_rows_keeps_its_own_window(tmp_path, writer, 
     assert float((inside - outside).abs().max() / inside.abs().max()) > 0.2
 
 
-@pytest.mark.parametrize("dim,rot,heads,kv", [(16, 8, 2, 1), (96, 32, 8, 1), (64, 64 - 2, 4, 2)])
+@pytest.mark.parametrize("dim,rot,heads,kv", [(16, 8, 2, 1), (96, 32, 6, 1), (64, 64 - 2, 4, 2)])
 def test_a_far_key_among_hundreds(tmp_path, dim, rot, heads, kv):
     cfg, patch = conv_needle_model(dim, rot, heads, kv)
     pcfg, w = make(cfg, tmp_path, seed=22, std=0.05, norm_std=0.0, patch=patch)
