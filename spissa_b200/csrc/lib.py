@@ -1227,7 +1227,8 @@ def moe_experts(x, ids, weights, w_gate_up, w_down, y, top, limit, slope=1.702, 
             TC_SILU_MUL, 2 * int(glu_block), c_void_p(_ptr(tab_up)), c_float(limit), c_float(slope), status, c_void_p(_stream())))
         _check("tc_gemm", tc.sp_tc_gemm_grouped(
             c_void_p(_ptr(act)), c_void_p(_ptr(w_down)), c_void_p(_ptr(out_rows)), dt_code(out_rows), rows, W, F, F, F, E * W, W,
-            TC_STORE, 128, c_void_p(_ptr(tab_down)), c_float(0.0), c_float(0.0), status, c_void_p(_stream())))
+            TC_STORE, 256 if W % 256 == 0 else 128, c_void_p(_ptr(tab_down)), c_float(0.0), c_float(0.0), status,
+            c_void_p(_stream())))
         _check("hybrid", lib.sp_moe_combine_rows(c_void_p(_ptr(out_rows)), c_void_p(_ptr(pos)), c_void_p(_ptr(weights)),
                                                  c_void_p(_ptr(y)), T, int(top), W, c_void_p(_stream())))
         return

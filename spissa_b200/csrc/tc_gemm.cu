@@ -194,6 +194,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr int TM = BM * CG;                                  // rows of a tile
     const int m_tiles = (M + TM - 1) / TM, n_tiles = (N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
+    // The order of the walk. A plain product takes the row tiles of a column tile one after another (the walkers of a
+    // moment share a few tiles of W). A grouped product takes the COLUMN tiles of a row tile one after another: the
+    // walkers of a moment then work on a few groups' weights, which the group's two or three row tiles share in L2,
+    // and every group's weights pass through once, instead of a slice of all groups' weights per wave.
+    const bool rows_outer = group != nullptr;
+    auto tile_m = [&](int tile) { return rows_outer ? tile / n_tiles : tile % m_tiles; };
+    auto tile_n = [&](int tile) { return rows_outer ? tile % n_tiles : tile / m_tiles; };
     const int rank = CG == 2 ? (int)pair_rank() : 0;
     const int walker = CG == 2 ? (int)blockIdx.x / 2 : (int)blockIdx.x;          // which of the tile walkers this CTA belongs to
     const int walkers = CG == 2 ? (int)gridDim.x / 2 : (int)gridDim.x;
@@ -239,9 +246,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t kbc = 0;                                   // pipeline slots used so far, over all tiles
             bool ok = true;
             for (int tile = walker; tile < total_tiles && ok; tile += walkers) {
-                const int w_row = group ? group[tile % m_tiles] : 0;
+                const int w_row = group ? group[tile_m(tile)] : 0;
                 if (w_row < 0) continue;
-                const int m0 = (tile % m_tiles) * TM + rank * BM, n0 = (tile / m_tiles) * BN + rank * (BN / CG);
+                const int m0 = tile_m(tile) * TM + rank * BM, n0 = tile_n(tile) * BN + rank * (BN / CG);
                 for (int kb = 0; kb < num_kb; ++kb, ++kbc) {
                     const int s = kbc % STAGES;
                     const uint32_t phase = (kbc / STAGES) & 1u;
@@ -269,7 +276,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t kbc = 0, it = 0;
             bool ok = true;
             for (int tile = walker; tile < total_tiles && ok; tile += walkers, ++it) {
-                if (group && group[tile % m_tiles] < 0) { --it; continue; }      // not in use: no accumulator is taken
+                if (group && group[tile_m(tile)] < 0) { --it; continue; }      // not in use: no accumulator is taken
                 const uint32_t buf = it & 1u, use = it >> 1;
                 ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), (use & 1u) ^ 1u, status, 104);
                 if (!ok) break;
@@ -306,8 +313,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             else mbar_arrive(smem_u32(&bar_acc_empty[buf]));
         };
         for (int tile = walker; tile < total_tiles; tile += walkers, ++it) {
-            if (group && group[tile % m_tiles] < 0) { --it; continue; }
-            const int m0 = (tile % m_tiles) * TM + rank * BM, n0 = (tile / m_tiles) * BN;
+            if (group && group[tile_m(tile)] < 0) { --it; continue; }
+            const int m0 = tile_m(tile) * TM + rank * BM, n0 = tile_n(tile) * BN;
             const uint32_t buf = it & 1u, use = it >> 1;
             const int row = m0 + q * 32 + lane;
             constexpr int SPAN = 32;
@@ -496,7 +503,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     s_row += __shfl_xor_sync(0xffffffffu, s_row, 2);
                     s_row += __shfl_xor_sync(0xffffffffu, s_row, 4);
                     if ((lane & 7) == 0 && sub + 4 * k < rows_here)
-                        ep.ssq_out[(size_t)(m0 + q * 32 + sub + 4 * k) * n_tiles + (tile / m_tiles)] = s_row;
+                        ep.ssq_out[(size_t)(m0 + q * 32 + sub + 4 * k) * n_tiles + tile_n(tile)] = s_row;
                 }
                 continue;
             }
