@@ -1188,14 +1188,14 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int* 
     }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict__ counts, int E, int* __restrict__ sorted,
                  int* __restrict__ tiles /* [max_tiles][3] */, int max_tiles, int tm, int padded, int* __restrict__ pos,
                  int* __restrict__ tab_up, int* __restrict__ tab_down, int up_rows, int down_rows) {
     // ``padded``: every expert's rows begin at a tile's first row (the sorted list then has holes, which say -1, and
     // ``pos`` gives every pair its row); ``tab_up`` / ``tab_down``: per tile the row at which the expert's matrices begin
     // in the stacked weights (-1: the tile is not in use), for products that take whole tiles of one expert.
-    __shared__ int start, tile0, mine, wsum[8], running;
+    __shared__ int start, tile0, mine, wsum[32], running;     // blocks of up to 1,024 threads: a pass of the list per 1,024 pairs
     const int e = blockIdx.x;
     if (threadIdx.x == 0) {
         int s = 0, t0 = 0;
@@ -1204,7 +1204,8 @@ moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int base = 0; base < n_pairs; base += 256) {
+    const int n_warps = (int)(blockDim.x >> 5);
+    for (int base = 0; base < n_pairs; base += (int)blockDim.x) {
         const int p = base + threadIdx.x;
         const bool hit = p < n_pairs && ids[p] == e;
         const unsigned b = __ballot_sync(0xffffffffu, hit);
@@ -1220,7 +1221,7 @@ moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict
         __syncthreads();
         if (threadIdx.x == 0) {
             int tot = 0;
-            for (int w = 0; w < 8; ++w) tot += wsum[w];
+            for (int w = 0; w < n_warps; ++w) tot += wsum[w];
             running += tot;
         }
         __syncthreads();
@@ -1246,7 +1247,7 @@ static int moe_plan(const int* ids, int n_pairs, int E, int* counts, int* sorted
                     cudaStream_t stream) {
     moe_count_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts);
     SP_CHECK_LAUNCH("moe_count");
-    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, tm, 0, nullptr, nullptr, nullptr, 0, 0);
+    moe_place_kernel<<<E, n_pairs >= 2048 ? 1024 : 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, tm, 0, nullptr, nullptr, nullptr, 0, 0);
     SP_CHECK_LAUNCH("moe_place");
     return 0;
 }
@@ -1273,7 +1274,7 @@ SP_API int sp_moe_plan_tiles(const void* x, const int* ids, int T, int top, int 
     SP_CHECK_CALL("moe_plan_tiles", cudaMemsetAsync(sorted, 0xff, (size_t)max_tiles * 128 * sizeof(int), stream));
     moe_count_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts);
     SP_CHECK_LAUNCH("moe_count");
-    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, 128, 1, pos, tab_up, tab_down, up_rows, down_rows);
+    moe_place_kernel<<<E, n_pairs >= 2048 ? 1024 : 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, 128, 1, pos, tab_up, tab_down, up_rows, down_rows);
     SP_CHECK_LAUNCH("moe_place");
     const size_t n = (size_t)max_tiles * 128 * (W / 8);
     const size_t want = (n + 255) / 256;
