@@ -474,7 +474,8 @@ def kugirax_rooflines(size, kx, row, T, peaks, eb) -> dict:
     out["key and value expansion (tensor)"] = dict(ms=kz.get("key_value_expansion_ms"),
                                                    frac=frac(n_lat * T * 2.0 * r * lh * (ld + lvd), tf, kz.get("key_value_expansion_ms")))
     hp = (kz.get("query_into_latent_space_ms") or 0) + (kz.get("value_expansion_ms") or 0)
-    out["per-head products (tensor)"] = dict(ms=hp, frac=frac(n_lat * T * lh * 2.0 * r * (ld + lvd), tf, hp))
+    if hp:                                                   # only steps that attend over the cached rows run them
+        out["per-head products (tensor)"] = dict(ms=hp, frac=frac(n_lat * T * lh * 2.0 * r * (ld + lvd), tf, hp))
     out["latent norms+append (hbm)"] = dict(ms=kz.get("latent_norm+append_ms"),
                                             frac=frac((T * (qr + r) * 4.0 + T * (qr + r) * eb) + T * qr * (4.0 + eb), bw,
                                                       kz.get("latent_norm+append_ms")))
