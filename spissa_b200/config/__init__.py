@@ -6,8 +6,10 @@ from .llama import ConfigError, LlamaConfig, RopeScaling
 from .duzinex import DuzinexConfig
 from .gozatar import GozatarConfig
 from .kugirax import KugiraxConfig
+from .fotulix import FotulixConfig
 
 __all__ = ["LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule",
            "UnknownArchitecture", "config_class_for", "config_from_dict", "known_architectures",
            "load_config", "register_architecture", "unregister_architecture",
-           "ConfigError", "LlamaConfig", "RopeScaling", "DuzinexConfig", "GozatarConfig", "KugiraxConfig"]
+           "ConfigError", "LlamaConfig", "RopeScaling", "DuzinexConfig", "GozatarConfig", "KugiraxConfig",
+           "FotulixConfig"]

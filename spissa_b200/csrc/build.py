@@ -57,6 +57,7 @@ MODULES = {
     "diff_flash": "diff_flash.cu",
     "hybrid": "hybrid_kernels.cu",
     "latent": "latent_kernels.cu",
+    "sandwich": "sandwich_kernels.cu",
 }
 
 

@@ -571,7 +571,9 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
 // owns output dims d, d+32, ... . A token at position p sees keys lo..p with
 // lo = max(0, p-window+1) when window > 0, else 0. All keys, this step's included,
 // are read from the cache. ``sink`` (float32 per query head, or null): a score that joins the
-// softmax's denominator once and has no value row.
+// softmax's denominator once and has no value row. ``dist_bias`` (float32 [heads][dist_cap + 1], or null): a score
+// added for the distance between query and key, distances beyond dist_cap taking the last entry; the scale does not
+// multiply it.
 
 // q · k over hd dims for one key row; 16-byte loads where the row allows them
 __device__ __forceinline__ float ag_dot(const float* __restrict__ qv, const float* __restrict__ kr, int hd) {
@@ -612,7 +614,7 @@ template <typename TQ, typename TC, bool SPLIT>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
                          TQ* __restrict__ out, KvPlace pl, int T, int nh, int nkv, int hd, int vd, int window,
-                         float scale, const float* __restrict__ sink) {
+                         float scale, const float* __restrict__ sink, const float* __restrict__ dist_bias, int dist_cap) {
     __shared__ __align__(16) float qs[AG_WARPS][AG_MAX_HD];
     __shared__ float part_ml[AG_WARPS][2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -644,6 +646,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
             my_off = j % ps;
             const TC* kr = kpool + (((size_t)my_page * nkv + g) * ps + my_off) * hd;
             s = ag_dot(qs[warp], kr, hd) * scale;
+            if (dist_bias) s += dist_bias[(size_t)h * (dist_cap + 1) + min(p - j, dist_cap)];
         }
         const float m_new = fmaxf(m, sp_warp_max(s));
         const float e = valid ? expf(s - m_new) : 0.0f;
@@ -725,8 +728,10 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, const void* vpool, int cache_dt,
                                 void* out, const int* token_seq, const int* positions, const int* seq_slot,
                                 const int* page_table, int max_pages, int page_size, int T, int nh, int nkv,
-                                int hd, int vd, int window, float scale, const float* sink, cudaStream_t stream) {
+                                int hd, int vd, int window, float scale, const float* sink, const float* dist_bias,
+                                int dist_cap, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (dist_bias && dist_cap < 0) SP_FAIL("attention: a distance-bias table needs at least one entry per head");
     if (hd <= 0 || hd > AG_MAX_HD) SP_FAIL("attention: head_dim %d is beyond this kernel's limit %d", hd, AG_MAX_HD);
     if (vd <= 0 || vd > AG_MAX_HD) SP_FAIL("attention: value size %d is beyond this kernel's limit %d", vd, AG_MAX_HD);
     if (nkv <= 0 || nh % nkv) SP_FAIL("attention: %d heads are no multiple of %d kv heads", nh, nkv);
@@ -739,9 +744,9 @@ SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, cons
 #define AG_LAUNCH(TQ, TC)                                                                                              \
     do {                                                                                                               \
         if (split)                                                                                                     \
-            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink); \
+            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink, dist_bias, dist_cap); \
         else                                                                                                           \
-            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink); \
+            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink, dist_bias, dist_cap); \
     } while (0)
     if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) AG_LAUNCH(float, float);
     else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) AG_LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -176,11 +176,26 @@ def rope_kv_write(qkv, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd, rd, w
         c_void_p(_ptr(inv_freq)), T, nh, nkv, hd, rd, int(bool(write_kv)), c_void_p(_stream())))
 
 
-def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale, vd=None, sink=None):
+FLASH_DISTANCE_BIAS = False      # whether the tensor-core attention kernels take a table of scores by distance
+
+
+def _dist_bias_args(dist_bias, nh):
+    """(pointer, last distance with an entry of its own) of a per-head table of scores by distance, float32
+    [nh, entries]: a key at distance n takes entry min(n, entries − 1)."""
+    if dist_bias is None:
+        return c_void_p(None), 0
+    if dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[0] != nh or not dist_bias.is_contiguous():
+        raise KernelError("attention: the distance bias is a contiguous float32 table [heads, distances]")
+    return c_void_p(_ptr(dist_bias)), int(dist_bias.shape[1]) - 1
+
+
+def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale, vd=None, sink=None, dist_bias=None):
     """Causal attention of every token of the step over its sequence's cached keys; ``vd``: the size of a value row
     when it differs from a key row's (``out`` is then [T, nh·vd]). ``sink`` (float32 [nh]): per head a score that joins
-    the softmax's denominator once and has no value."""
+    the softmax's denominator once and has no value. ``dist_bias`` (float32 [nh, entries]): a score added by the
+    distance between query and key, beyond the scale."""
     lib = load("generic")
+    bias_ptr, bias_cap = _dist_bias_args(dist_bias, nh)
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nh):
         raise KernelError("attention: the sinks are one float32 per query head")
     T = q.shape[0]
@@ -191,7 +206,8 @@ def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale, 
         c_void_p(_ptr(q)), dt_code(q), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool),
         c_void_p(_ptr(out)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)),
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
-        T, nh, nkv, hd, int(vd or hd), int(window or 0), c_float(scale), c_void_p(_ptr(sink)), c_void_p(_stream())))
+        T, nh, nkv, hd, int(vd or hd), int(window or 0), c_float(scale), c_void_p(_ptr(sink)), bias_ptr, bias_cap,
+        c_void_p(_stream())))
 
 
 def softcap(x, cap: float):
@@ -1315,3 +1331,87 @@ def latent_flash(qc, pool, out, meta, step, H, rank, window, scale, sink=None, m
     if need:
         global launches
         launches += 1        # two kernels: the shares and their combination
+
+
+# ------------------------------------------------------------------ sandwich: sublayers between two norms, gated attention rows
+def pair_embed(table, pairs, step, state, out, buckets, mul_prev, mul_cur, scale, status=None):
+    """out[t,:] (float32) = table[id_t,:] · scale + pairs[(id_{t−1} · mul_prev + id_t · mul_cur) mod buckets, :]; a
+    sequence's first token takes row ``buckets``. ``state`` int32 [slots]: the token before a step's first one; the
+    kernel leaves the step's last token there."""
+    lib = load("sandwich")
+    T, W = out.shape
+    _need_contig(table, pairs, out, state)
+    if table.dtype != pairs.dtype or pairs.shape != (int(buckets) + 1, W) or state.dtype != torch.int32:
+        raise KernelError("pair_embed: the pair table is [buckets + 1, width] of the token table's type, the state int32")
+    _check("sandwich", lib.sp_pair_embed(
+        c_void_p(_ptr(table)), c_void_p(_ptr(pairs)), dt_code(table), c_void_p(_ptr(step.tokens)), c_void_p(_ptr(step.positions)),
+        c_void_p(_ptr(step.token_seq)), c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), c_void_p(_ptr(state)),
+        state.numel(), c_void_p(_ptr(out)), T, W, table.shape[0], int(buckets), int(mul_prev), int(mul_cur), c_float(scale),
+        c_void_p(_ptr(status)), c_void_p(_stream())))
+
+
+def stream_norm_add(x, y, w_post, mult, eps, w_next=None, out=None, raw=False):
+    """x ← x + mult · y / sqrt(mean(y²) + eps) ⊙ w_post, row by row, and y ← 0 (x, y float32 [T, W]; the weights
+    float32 as they multiply). ``out`` [T, W] then receives the next reader's input: the RMS norm of the new x with
+    ``w_next``, or with ``raw`` the new x itself."""
+    lib = load("sandwich")
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or w_post.dtype != torch.float32 or x.shape != y.shape:
+        raise KernelError("stream_norm_add works on two float32 buffers of one shape and float32 weights")
+    _need_contig(x, y, w_post, w_next, out)
+    mode = 0 if out is None else (2 if raw else 1)
+    if mode == 1 and (w_next is None or w_next.dtype != torch.float32):
+        raise KernelError("stream_norm_add: the next norm needs a float32 weight")
+    _check("sandwich", lib.sp_stream_norm_add(
+        c_void_p(_ptr(x)), c_void_p(_ptr(y)), c_void_p(_ptr(w_post)), c_void_p(_ptr(w_next)), c_void_p(_ptr(out)),
+        dt_code(out) if out is not None else 0, mode, x.shape[0], x.shape[1], c_float(mult), c_float(eps), c_void_p(_stream())))
+
+
+def gated_qkv_store(proj, bias, q_out, k_pool, v_pool, meta, gates, freq, nh, nkv, d, vd, rd, write_kv=True, rot_mult=1.0,
+                    temp_coef=0.0, temp_every=1):
+    """``proj`` rows (float32) = [q: nh·d | k: nkv·d | v: nkv·vd | gates: nh]: add ``bias`` (over q, k, v), multiply q by
+    1 + temp_coef · ln(floor((position + 1) / temp_every) + 1), rotate neighbouring pairs over the first ``rd`` dims of
+    every q and k head by position · freq[i] (cos and sin times ``rot_mult``), store q to ``q_out``, k and v into their
+    page rows and the gates' arguments to ``gates`` (float32 [T, nh], or None)."""
+    lib = load("sandwich")
+    if proj.dtype != torch.float32:
+        raise KernelError("gated_qkv_store reads 32-bit projections")
+    _need_contig(proj, bias, q_out, gates, freq)
+    pt = meta.page_table
+    _declare_bounds("sandwich", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), proj.device)
+    _check("sandwich", lib.sp_gated_qkv_store(
+        c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(bias)), dt_code(bias) if bias is not None else 0, c_void_p(_ptr(q_out)),
+        dt_code(q_out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool), c_void_p(_ptr(gates)), c_void_p(_ptr(freq)),
+        c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)),
+        pt.shape[1], meta.page_size, proj.shape[0], int(nh), int(nkv), int(d), int(vd), int(rd), int(bool(write_kv)),
+        c_float(rot_mult), c_float(temp_coef), int(temp_every), c_void_p(_stream())))
+
+
+def latent_rot_store(proj, wc, q_out, pool, meta, gates, freq, H, d, rd, rank, rot_mult, eps, rows_out=None):
+    """``proj`` rows (float32) = [q: H·(d + rd) | row: rank | key part: rd | gates: H] (``pool`` None: no row and no key
+    part). The row's RMS norm with ``wc`` and the key part with its neighbouring pairs rotated go into ONE page row
+    [rank + rd] of ``pool``; every head's last ``rd`` query dims are rotated the same way; q to ``q_out``, the gates'
+    arguments to ``gates`` (float32 [T, H]). ``rows_out`` [T, rank + rd] also receives the page rows token by token."""
+    lib = load("sandwich")
+    if proj.dtype != torch.float32:
+        raise KernelError("latent_rot_store reads 32-bit projections")
+    _need_contig(proj, wc, q_out, gates, freq, rows_out)
+    pt = meta.page_table
+    if pool is not None:
+        _declare_bounds("sandwich", lib, _pool_pages(meta, pool), _table_rows(meta, pt), proj.device)
+    _check("sandwich", lib.sp_latent_rot_store(
+        c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(wc)), dt_code(wc) if wc is not None else 0, c_void_p(_ptr(q_out)),
+        dt_code(q_out), c_void_p(_ptr(pool)), dt_code(pool) if pool is not None else 0, c_void_p(_ptr(rows_out)),
+        c_void_p(_ptr(gates)), c_void_p(_ptr(freq)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)),
+        c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, proj.shape[0], int(H), int(d), int(rd),
+        int(rank), c_float(rot_mult), c_float(eps), c_void_p(_stream())))
+
+
+def gelu_gather_mul(z, table, ids, out, offset):
+    """out[t, j] = gelu_tanh(z[t, j]) · table[ids[t], offset + j] for z, out [T, C]."""
+    lib = load("sandwich")
+    _need_contig(z, table, ids, out)
+    if z.shape != out.shape or z.dtype != out.dtype:
+        raise KernelError("gelu_gather_mul: input and output are one shape and type")
+    _check("sandwich", lib.sp_gelu_gather_mul(
+        c_void_p(_ptr(z)), dt_code(z), c_void_p(_ptr(table)), dt_code(table), c_void_p(_ptr(ids)), c_void_p(_ptr(out)),
+        z.shape[0], z.shape[1], table.shape[1], int(offset), table.shape[0], c_void_p(_stream())))

@@ -17,6 +17,9 @@ from ..phases import phase, profiling
 from ..csrc import lib as K
 
 
+EMBEDDING_CACHE = "embedding"      # the cache id of what the embedding keeps per sequence
+
+
 class Model:
     def __init__(self, spec: ModelSpec):
         spec.validate()
@@ -94,6 +97,11 @@ class Model:
         for e in self.spec.schedule:
             if e.writes_cache:
                 out[e.cache] = self.layers[e.layer].cache_request()
+        # an embedding that keeps something per sequence (the token before the step) has a cache of its own
+        ask = getattr(self.embedding, "cache_request", None)
+        self._embedding_cache = ask() if ask is not None else None
+        if self._embedding_cache is not None:
+            out[EMBEDDING_CACHE] = self._embedding_cache
         return out
 
     def _host_runner(self, step, cache) -> bool:
@@ -118,7 +126,10 @@ class Model:
             h = None                                       # the kernel gathers the embedding rows itself
         else:
             with phase("embedding_ms"):
-                h = self.embedding.forward(step)
+                if getattr(self, "_embedding_cache", None) is not None:
+                    h = self.embedding.forward(step, cache.view(EMBEDDING_CACHE, step, True))
+                else:
+                    h = self.embedding.forward(step)
         if self.spec.streams > 1 and h is not None:
             streams = torch.empty(h.shape[0], self.spec.streams * h.shape[1], dtype=torch.float32, device=h.device)
             K.streams_expand(h, streams, self.spec.streams)        # every stream starts as the embedding's output

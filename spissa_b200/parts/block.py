@@ -203,3 +203,64 @@ class HyperConnectionBlock(Block):
         self.ffn.forward(x, step, y)
         with phase("streams_update_ms"):
             K.streams_norm(h, S, W, y=y, mix=c["mix2"], out_coef=c["out2"])
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Block):
+    """Every sublayer between two norms, its normed output scaled into the stream (not in the reference):
+
+        h ← h + r · n_1b(mixer(n_1(h)));   h ← h + r · n_2b(ffn(n_2(h)));   h ← h + r · n_s(side(h))
+
+    with r = ``residual_mult``. The feed-forward and the ``side`` sublayer (a feed-forward part that reads the stream
+    itself, not a norm of it) may be absent. ``norms`` has the places ``mixer``, ``mixer_out``, ``ffn``, ``ffn_out``
+    and ``side_out``; all are RMS norms (they hand their multiplying weight to the kernel that applies them). The
+    sublayers keep their interface: they ADD into a 32-bit row buffer that is zero when they get it; one kernel takes
+    the buffer's norm into the stream, leaves it zeroed and writes the next sublayer's input in the same pass."""
+    graph_safe = True
+    kernel_modules = ("sandwich",)
+
+    def __init__(self, mixer, ffn, norms: dict, hidden_size: int, residual_mult: float = 1.0, side=None, prefix: str = ""):
+        super().__init__(prefix)
+        self.hidden_size, self.residual_mult = int(hidden_size), float(residual_mult)
+        self.mixer = build_part("mixer", mixer)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.side = build_part("ffn", side) if side is not None else None
+        self.mixer_norm, self.mixer_out = build_part("norm", norms["mixer"]), build_part("norm", norms["mixer_out"])
+        self.ffn_norm = build_part("norm", norms["ffn"]) if ffn is not None else None
+        self.ffn_out = build_part("norm", norms["ffn_out"]) if ffn is not None else None
+        self.side_out = build_part("norm", norms["side_out"]) if side is not None else None
+        for n in (self.mixer_norm, self.mixer_out, self.ffn_norm, self.ffn_out, self.side_out):
+            if n is not None and not hasattr(n, "multiplier"):
+                raise ValueError(f"{prefix}: the norms of this arrangement are RMS norms")
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_out, self.ffn_norm, self.ffn, self.ffn_out, self.side,
+                            self.side_out) if p is not None]
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, h, step, cache):
+        W, r = self.hidden_size, self.residual_mult
+        y = step.scratch.get("sublayer_sum")
+        if y is None or y.shape[1] != W:
+            y = step.scratch["sublayer_sum"] = torch.zeros(h.shape[0], W, dtype=torch.float32, device=h.device)
+        with phase("attention_norm_ms"):
+            x = self.mixer_norm.forward(h)
+        self.mixer.forward(x, step, cache, y)
+        last = self.mixer_out
+        if self.ffn is not None:
+            with phase("attention_out_norm+mlp_norm_ms"):
+                x = torch.empty(h.shape[0], W, dtype=self.rt.act_dtype, device=h.device)
+                K.stream_norm_add(h, y, last.multiplier(), r, last.eps, w_next=self.ffn_norm.multiplier(), out=x)
+            self.ffn.forward(x, step, y)
+            last = self.ffn_out
+        with phase("out_norm_ms"):
+            if self.side is None:
+                K.stream_norm_add(h, y, last.multiplier(), r, last.eps)
+                return
+            x = torch.empty(h.shape[0], W, dtype=self.rt.act_dtype, device=h.device)
+            K.stream_norm_add(h, y, last.multiplier(), r, last.eps, out=x, raw=True)     # the side sublayer reads the stream itself
+        self.side.forward(x, step, y)
+        with phase("side_out_norm_ms"):
+            K.stream_norm_add(h, y, self.side_out.multiplier(), r, self.side_out.eps)

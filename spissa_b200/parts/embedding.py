@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib as K
-from .base import Part, WeightSpec
+from .base import Part, StateRequest, WeightSpec
 from .linear import Linear
 from .registry import register_part
 
@@ -48,6 +48,49 @@ class TokenEmbedding(Part):
         ids = step.tokens
         out = torch.empty(ids.shape[0], self.hidden_size, dtype=torch.float32, device=ids.device)
         K.embed_gather(self.weight, ids, out, K.status_word(ids.device), self.scale)
+        return out
+
+
+@register_part("embedding", "pair_embedding")
+class PairEmbedding(TokenEmbedding):
+    """The token's row times ``scale`` plus a row of a second table chosen by the token and the one before it (not in
+    the reference): row (id_{t−1} · mul_prev + id_t · mul_cur) mod buckets of ``pair_name`` [buckets + 1, hidden]; a
+    sequence's first token has no token before it and takes the last row. The token before a step's first one is a
+    word of per-slot state (``cache_request``): the kernel reads it and leaves the step's last token there."""
+    graph_safe = True
+    kernel_modules = ("sandwich",)
+
+    def __init__(self, vocab_size: int, hidden_size: int, buckets: int, mul_prev: int, mul_cur: int, prefix: str = "",
+                 weight_name: str = "weight", pair_name: str = "pairs", scale: float = 1.0):
+        super().__init__(vocab_size, hidden_size, prefix, weight_name, scale)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        if self.buckets <= 0:
+            raise ValueError(f"{prefix}: the pair table needs at least one bucket")
+        self.pair_name = prefix + pair_name
+        self.pairs = None
+
+    def weight_specs(self):
+        return super().weight_specs() + [WeightSpec(self.pair_name, (self.buckets + 1, self.hidden_size))]
+
+    def cache_request(self):
+        return StateRequest((1,), torch.int32)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.pairs = tensors[self.pair_name].contiguous()
+        if self.pairs.dtype != self.weight.dtype:
+            raise ValueError(f"{self.prefix}: the token table and the pair table must share a storage type")
+
+    def fused_fields(self):
+        return None
+
+    def forward(self, step, cache=None) -> torch.Tensor:
+        if cache is None:
+            raise ValueError(f"{self.prefix}: this embedding needs its per-slot state (the token before the step)")
+        ids = step.tokens
+        out = torch.empty(ids.shape[0], self.hidden_size, dtype=torch.float32, device=ids.device)
+        K.pair_embed(self.weight, self.pairs, step, cache.state, out, self.buckets, self.mul_prev, self.mul_cur, self.scale,
+                     K.status_word(ids.device))
         return out
 
 

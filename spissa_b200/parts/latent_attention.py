@@ -182,3 +182,119 @@ class LatentAttention(Mixer):
             K.latent_flash(qc, cache.k_pool, mix, cache, step, H, r, self.window, self.scale, self.sink, max_len=max_len)
             return mix
         return attend_paged(qc, step, cache, H, 1, r, self.window, self.scale, self.sink, self.counters)
+
+
+@register_part("mixer", "rotary_latent_attention")
+class RotaryLatentAttention(Mixer):
+    """Attention through a cached low-rank row plus ONE rotated key part that all heads share, with a gate per head
+    (not in the reference).
+
+        q_h = [q_h° (dim) | q_h^r (rot_dim)] = W_q,h x,   q_h^r rotated (neighbouring pairs, the position part's
+                                                           frequencies, cos and sin times its amplitude)
+        [c° | k^r] = D x,   c = n(c°) ⊙ w_c  (rank),   k^r (rot_dim) rotated the same way: what is cached, ONE page row
+        score_h(i, j) = ((U_k,h c_j) · q_i,h° + k_j^r · q_i,h^r) · scale    over i − w < j <= i (``window`` w; None: all)
+        y += W_o · concat_h( sigmoid(w_g,h · x) · U_v,h Σ_j p_h(i, j) c_j )
+
+    Keys and values are never expanded. A page row is r_j = [c_j | k_j^r]; with the per-head map
+    E_h = [[U_k,hᵀ, 0], [0, I]] the score is (E_h q_i,h) · r_j, so the query is carried into the rows' space once per
+    token, the attention runs over the cached rows as they lie (one row is key and value, for all heads), and the
+    weighted sum of rows is expanded once per token by [U_v,h | 0]. A layer built with ``shares_latent`` has no D and
+    no norm weight: it reads the rows another layer cached (a run with ``cache.writes`` False), with its own q, U_k,
+    U_v, gates and window. ``cache_window``: the window the cache keeps rows for when readers with other windows
+    share it."""
+    graph_safe = True
+    kernel_modules = ("sandwich", "latent")
+    kernel_modules_bf16 = ("attention",)
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int, kv_rank: int,
+                 scale: float, eps: float, position=None, window=None, cache_window=_UNSET, shares_latent: bool = False,
+                 prefix: str = "", names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.head_dim, self.rot_dim, self.v_head_dim, self.kv_rank = int(head_dim), int(rot_dim), int(v_head_dim), int(kv_rank)
+        self.scale, self.eps = float(scale), float(eps)
+        self.window = int(window) if window else None
+        self.cache_window = self.window if cache_window is _UNSET else (int(cache_window) if cache_window else None)
+        if self.cache_window is not None and (self.window is None or self.window > self.cache_window):
+            raise ValueError(f"{prefix}: a window of {self.window} sees rows that a cache of {self.cache_window} has returned")
+        self.shares_latent = bool(shares_latent)
+        n = dict(q="q", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", g="g", o="o")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        from .registry import build_part
+        self.position = build_part("position", position) if position is not None else None
+        if self.rot_dim and (self.position is None or getattr(self.position, "pairing", "half") != "interleaved"
+                             or self.position.rotary_dim != self.rot_dim):
+            raise ValueError(f"{prefix}: the rotated part of {self.rot_dim} dims needs a rotary part of that size with pairing 'interleaved'")
+        self.proj = self.o = self.wc_norm = self.q_map = self.v_map = None
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def weight_specs(self):
+        W, H, d, rd, vd, r = self.hidden_size, self.num_heads, self.head_dim, self.rot_dim, self.v_head_dim, self.kv_rank
+        n = self.names
+        specs = [WeightSpec(n["q"], (H * (d + rd), W)), WeightSpec(n["uk"], (H * d, r)), WeightSpec(n["uv"], (H * vd, r)),
+                 WeightSpec(n["g"], (H, W)), WeightSpec(n["o"], (W, H * vd))]
+        if not self.shares_latent:
+            specs += [WeightSpec(n["dkv"], (r + rd, W)), WeightSpec(n["dkv_norm"], (r,), init="ones")]
+        return specs
+
+    def cache_request(self):
+        return KVCacheRequest(1, self.kv_rank + self.rot_dim, self.cache_window, keys_only=True)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        n = self.names
+        H, d, rd, vd, r = self.num_heads, self.head_dim, self.rot_dim, self.v_head_dim, self.kv_rank
+        q, g = tensors[n["q"]], tensors[n["g"]]
+        stack = [q, g] if self.shares_latent else [q, tensors[n["dkv"]], g]
+        if len({p.dtype for p in stack}) != 1:
+            raise ValueError(f"{self.prefix}: the projections of one input must share a storage type")
+        self.proj = Linear(torch.cat(stack, dim=0))                # rows [q | (c° | k^r) | gates]
+        self.wc_norm = None if self.shares_latent else tensors[n["dkv_norm"]].contiguous()
+        uk, uv = tensors[n["uk"]], tensors[n["uv"]]
+        R = r + rd
+        # E_h [R, d + rd]: rows of the cached row's space, stored [out, in] like every weight (exact: ones and zeros)
+        q_map = torch.zeros(H, R, d + rd, dtype=uk.dtype, device=uk.device)
+        q_map[:, :r, :d] = uk.view(H, d, r).transpose(1, 2)
+        if rd:
+            q_map[:, r:, d:] = torch.eye(rd, dtype=uk.dtype, device=uk.device)
+        self.q_map = q_map.contiguous()
+        v_map = torch.zeros(H, vd, R, dtype=uv.dtype, device=uv.device)      # [U_v,h | 0]
+        v_map[:, :, :r] = uv.view(H, vd, r)
+        self.v_map = v_map.contiguous()
+        self.o = Linear(tensors[n["o"]])
+        self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
+
+    def forward(self, x, step, cache, residual):
+        H, d, rd, vd, r = self.num_heads, self.head_dim, self.rot_dim, self.v_head_dim, self.kv_rank
+        T, dev, act, R = x.shape[0], x.device, self.rt.act_dtype, self.kv_rank + self.rot_dim
+        writes = cache.writes
+        if writes and self.shares_latent:
+            raise ValueError(f"{self.prefix}: a layer without a latent projection cannot be the writer of a cache")
+        freq, amp = (self.position.rotary()[0], getattr(self.position, "amplitude", 1.0)) if rd else (None, 1.0)
+        with phase("latent_projection_ms"):
+            proj = self.proj(x, out_dtype=torch.float32)            # norm and rotation read unrounded products
+        with phase("latent_norm+rotary+append_ms"):
+            q = torch.empty(T, H * (d + rd), dtype=act, device=dev)
+            gates = torch.empty(T, H, dtype=torch.float32, device=dev)
+            K.latent_rot_store(proj, self.wc_norm if writes else None, q, cache.k_pool if writes else None, cache, gates, freq,
+                               H, d, rd, r, amp, self.eps)
+        with phase("query_into_latent_space_ms"):
+            qx = torch.empty(T, H * R, dtype=act, device=dev)
+            K.headwise_product(q, self.q_map, qx, H, d + rd, R, w_rows_are_k=False)              # E_h q_h
+        with phase("latent_attention_ms"):
+            if act == torch.bfloat16 and cache.k_pool.dtype == torch.bfloat16 and K.latent_flash_supported(R, cache.page_size):
+                mix = torch.empty_like(qx)
+                max_len = length_bucket(step.max_len, cache.page_size) if step.all_single else None
+                K.latent_flash(qx, cache.k_pool, mix, cache, step, H, R, self.window, self.scale, None, max_len=max_len)
+            else:
+                mix = attend_paged(qx, step, cache, H, 1, R, self.window, self.scale, None, self.counters)
+        with phase("value_expansion_ms"):
+            ctx = torch.empty(T, H * vd, dtype=act, device=dev)
+            K.headwise_product(mix, self.v_map, ctx, H, R, vd, w_rows_are_k=False)               # U_v,h (Σ p c)
+        with phase("head_gate_ms"):
+            K.scale_rows_sigmoid(ctx.view(T * H, vd), gates.view(T * H))
+        with phase("o_projection+attention_residual_ms"):
+            self.o(ctx, out=residual, accumulate=True)

@@ -279,3 +279,43 @@ class RoutedExperts(FeedForward):
             self.shared.forward(x, step, residual, row_gate=gate)
         elif self.shared is not None:
             self.shared.forward(x, step, residual)
+
+
+@register_part("ffn", "token_side")
+class TokenSideInput(FeedForward):
+    """A per-layer input chosen by the token (not in the reference): y += P · (gelu(G x) ⊙ S[id_t, offset : offset + dim])
+    with S a table [vocab, table_width] that several layers share (each reads its own columns), G [dim, hidden],
+    P [hidden, dim] and the tanh form of gelu. ``x`` is whatever the arrangement hands it (the stream itself)."""
+    graph_safe = True
+    kernel_modules = ("sandwich",)
+
+    def __init__(self, hidden_size: int, dim: int, vocab_size: int, table_width: int, offset: int, table_name: str,
+                 prefix: str = "", names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.dim, self.vocab_size = int(hidden_size), int(dim), int(vocab_size)
+        self.table_width, self.offset = int(table_width), int(offset)
+        if self.offset < 0 or self.offset + self.dim > self.table_width:
+            raise ValueError(f"{prefix}: columns {self.offset}..{self.offset + self.dim} lie outside a table of width {self.table_width}")
+        self.table_name = table_name                        # not under the prefix: the table belongs to all its readers
+        n = dict(gate="gate", proj="proj")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.table = self.gate = self.proj = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.table_name, (self.vocab_size, self.table_width)),
+                WeightSpec(self.names["gate"], (self.dim, self.hidden_size)),
+                WeightSpec(self.names["proj"], (self.hidden_size, self.dim))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.table = tensors[self.table_name].contiguous()
+        self.gate, self.proj = Linear(tensors[self.names["gate"]]), Linear(tensors[self.names["proj"]])
+
+    def forward(self, x, step, residual):
+        with phase("side_gate_ms"):
+            z = self.gate(x)
+            g = torch.empty_like(z)
+            K.gelu_gather_mul(z, self.table, step.tokens, g, self.offset)
+        with phase("side_projection_ms"):
+            self.proj(g, out=residual, accumulate=True)

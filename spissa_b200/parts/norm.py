@@ -24,19 +24,31 @@ from .registry import register_part
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, size: int, eps: float, prefix: str = "", weight_name: str = "weight"):
+    def __init__(self, size: int, eps: float, prefix: str = "", weight_name: str = "weight", around_zero: bool = False):
         super().__init__(prefix)
         self.size = int(size)
         self.eps = float(eps)
         self.weight_name = prefix + weight_name
+        self.around_zero = bool(around_zero)   # the stored weight w lies around zero and 1 + w multiplies (not in the reference)
         self.weight = None
 
     def weight_specs(self):
-        return [WeightSpec(self.weight_name, (self.size,), init="ones")]
+        return [WeightSpec(self.weight_name, (self.size,), init="normal" if self.around_zero else "ones")]
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.weight = tensors[self.weight_name].contiguous()
+        if self.around_zero:
+            self.weight = (1.0 + self.weight.float()).contiguous()     # 32-bit: 1 + w rounded to 16 bits would lose w
+
+    def multiplier(self) -> torch.Tensor:
+        """The weight as it multiplies, float32 [size] (for a kernel that applies this norm inside another pass)."""
+        if self.weight.dtype != torch.float32:
+            self.weight32 = getattr(self, "weight32", None)
+            if self.weight32 is None:
+                self.weight32 = self.weight.float().contiguous()
+            return self.weight32
+        return self.weight
 
     def fused_fields(self):
         if self.weight is None or self.weight.dtype != torch.bfloat16:

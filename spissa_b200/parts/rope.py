@@ -10,6 +10,11 @@ reference, which drops it: crates/spissa-import/src/safetensors.rs:163-175). Wit
 λ = 2π/inv_freq: λ > n0/low ⇒ inv_freq/factor; λ < n0/high ⇒ unchanged; between,
 (1−s)·inv_freq/factor + s·inv_freq with s = (n0/λ − low)/(high − low).
 ``linear`` divides every frequency by ``factor``.
+
+``ramp`` (not in the reference) interpolates pair by pair: with pair(t) = dims · ln(n0 / (2π t)) / (2 ln θ) the pair
+that turns t times over the original length n0, lo = max(⌊pair(fast)⌋, 0), hi = min(⌈pair(slow)⌉, dims − 1) and
+r_i = clamp((i − lo) / max(hi − lo, 0.001), 0, 1), pair i turns at inv_freq_i / factor · r_i + inv_freq_i · (1 − r_i),
+and cos and sin are both multiplied by the ``amplitude`` 0.1 · ln(factor) + 1. Computed in 64-bit, rounded once.
 """
 from __future__ import annotations
 
@@ -45,7 +50,27 @@ def rotary_inv_freq(theta: float, rotary_dim: int, scaling: dict | None) -> torc
         out = torch.where(wavelen > n0 / low, inv_freq / factor, inv_freq)
         medium = (wavelen <= n0 / low) & (wavelen >= n0 / high)
         return torch.where(medium, blended, out).to(torch.float32)
+    if kind == "ramp":
+        n0, fast, slow = float(scaling["original"]), float(scaling["fast"]), float(scaling["slow"])
+
+        def pair_of(turns: float) -> float:
+            return rotary_dim * math.log(n0 / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+        lo = max(math.floor(pair_of(fast)), 0)
+        hi = min(math.ceil(pair_of(slow)), rotary_dim - 1)
+        out = []
+        for i in range(rotary_dim // 2):
+            f = float(theta) ** (-2.0 * i / rotary_dim)
+            r = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+            out.append(f / factor * r + f * (1.0 - r))
+        return torch.tensor(out, dtype=torch.float64).to(torch.float32)
     raise ValueError(f"unsupported rope scaling type {kind!r}")
+
+
+def rotary_amplitude(scaling: dict | None) -> float:
+    """What multiplies cos and sin: 1, or 0.1 · ln(factor) + 1 for the ``ramp`` scaling."""
+    if scaling and scaling.get("rope_type", scaling.get("type")) == "ramp":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 @register_part("position", "rotary")
@@ -62,6 +87,7 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = int(rotary_dim)
         self.scaling = dict(scaling) if scaling else None
         self.inv_freq_host = rotary_inv_freq(self.theta, self.rotary_dim, self.scaling)
+        self.amplitude = rotary_amplitude(self.scaling)     # multiplies cos and sin (the kernel that rotates must take it)
         self.inv_freq = None
 
     def bind(self, tensors, rt):
