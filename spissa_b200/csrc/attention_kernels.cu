@@ -81,6 +81,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
     const int warp_hi = pos0 + warp * 16 + 15;                     // last key any row of this warp may see
     const int warp_lo = window > 0 ? pos0 + warp * 16 - window + 1 : 0;
     const bool warp_active = warp * 16 < n_rows;
+    const float* bias_row = kv.dist_bias ? kv.dist_bias + (size_t)h * (kv.dist_cap + 1) : nullptr;
 
     for (int j = j_lo; j <= j_hi; ++j) {
         const int stage = (j - j_lo) & 1;
@@ -99,10 +100,10 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
             const bool all_seen = tile_pos0 + KT - 1 <= pos0 + warp * 16 && (window <= 0 || tile_pos0 >= warp_hi - window + 1);
             if (all_seen)
                 flash_step<HD, 8, false>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, 0, tile_pos0, lo, hi,
-                                         scale_log2, o, m, l, lane);
+                                         scale_log2, o, m, l, lane, bias_row, kv.dist_cap);
             else
                 flash_step<HD, 8, true>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, 0, tile_pos0, lo, hi,
-                                        scale_log2, o, m, l, lane);
+                                        scale_log2, o, m, l, lane, bias_row, kv.dist_cap);
         }
         __syncthreads();
     }
@@ -257,6 +258,7 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
             asm volatile("ld.shared.b32 %0, [%1];" : "=r"(qb[kk][i][1]) : "r"(a + 16));
         }
 
+    const float* bias_group = kv.dist_bias ? kv.dist_bias + (size_t)g * G * (kv.dist_cap + 1) : nullptr;
     for (int j = j_first; j <= j_last; ++j) {
         const int it = j - j_first;
         const int stage = it % DEC_STAGES;
@@ -266,10 +268,10 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
         __syncwarp();
         if (j * KT + KT - 1 <= p && j * KT >= first_key)
             decode_step_t<HD, NH, false>(qb, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT,
-                                         first_key, p, scale_log2, o, m, l, lane);
+                                         first_key, p, scale_log2, o, m, l, lane, bias_group, kv.dist_cap, G);
         else
             decode_step_t<HD, NH, true>(qb, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT,
-                                        first_key, p, scale_log2, o, m, l, lane);
+                                        first_key, p, scale_log2, o, m, l, lane, bias_group, kv.dist_cap, G);
         __syncwarp();                                              // the stage is free for this warp's next fetch
     }
     cp_async_wait<0>();
@@ -386,13 +388,16 @@ int launch_flash_prefill_as(dim3 grid, cudaStream_t stream, const __nv_bfloat16*
 }  // namespace
 
 // ``sink`` (float32 per query head, or null): a score that joins every row's denominator once, with no key and no value
-SP_API int sp_flash_prefill_sink(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
+// ``dist_bias`` (float32 [nh][dist_cap + 1], or null): a score added by the distance between query and key
+SP_API int sp_flash_prefill_bias(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
                                  const int* positions, const int* seq_row, const int* page_table, int max_pages,
                                  int page_size, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
-                                 float scale, const float* sink, cudaStream_t stream) {
+                                 float scale, const float* sink, const float* dist_bias, int dist_cap, cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
     if (check_common(hd, nh, nkv, page_size)) return 1;
-    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host, sink};
+    if (dist_bias && dist_cap < 0) SP_FAIL("flash_prefill: a distance-bias table needs at least one entry per head");
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host, sink,
+               dist_bias, dist_cap};
     if (n_q_tiles > 65535) SP_FAIL("flash_prefill: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
     const float sl = scale * LOG2E;
@@ -407,6 +412,14 @@ SP_API int sp_flash_prefill_sink(const void* q, void* out, const void* kpool, co
     }
     SP_CHECK_LAUNCH("flash_prefill");
     return 0;
+}
+
+SP_API int sp_flash_prefill_sink(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
+                                 const int* positions, const int* seq_row, const int* page_table, int max_pages,
+                                 int page_size, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
+                                 float scale, const float* sink, cudaStream_t stream) {
+    return sp_flash_prefill_bias(q, out, kpool, vpool, seq_start, positions, seq_row, page_table, max_pages, page_size,
+                                 n_seqs, n_q_tiles, nh, nkv, hd, window, scale, sink, nullptr, 0, stream);
 }
 
 SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
@@ -453,19 +466,21 @@ SP_API long long sp_flash_decode_scratch_floats(int n_seqs, int nh, int hd, int 
     return (long long)n_seqs * nh * n_chunks * (hd + 2);
 }
 
-SP_API int sp_flash_decode_sink(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
+SP_API int sp_flash_decode_bias(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
                                 const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
                                 int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
                                 int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats, int* counters,
-                                const float* sink, cudaStream_t stream) {
+                                const float* sink, const float* dist_bias, int dist_cap, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (check_common(hd, nh, nkv, page_size)) return 1;
+    if (dist_bias && dist_cap < 0) SP_FAIL("flash decode: a distance-bias table needs at least one entry per head");
     if (nh / nkv > 16) SP_FAIL("flash decode: %d query heads per kv head, at most 16 fit one tile", nh / nkv);
     if (chunk_tiles <= 0 || n_chunks <= 0 || n_chunks > 65535) SP_FAIL("flash decode: bad chunking %d x %d", n_chunks, chunk_tiles);
     if (n_seqs > 65535) SP_FAIL("flash decode: %d sequences are beyond this kernel's grid", n_seqs);
     const long long need = sp_flash_decode_scratch_floats(n_seqs, nh, hd, n_chunks);
     if (scratch_floats < need) SP_FAIL("flash decode: scratch holds %lld floats, %lld are needed", scratch_floats, need);
-    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host, sink};
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host, sink,
+               dist_bias, dist_cap};
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)n_seqs * nh * n_chunks * hd;
     dim3 grid(n_chunks, nkv, n_seqs);
@@ -480,6 +495,16 @@ SP_API int sp_flash_decode_sink(const void* q, void* out, int out_dt, const void
         decode_combine_kernel<float><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (float*)out, n_chunks, hd, sink, nh);
     SP_CHECK_LAUNCH("decode_combine");
     return 0;
+}
+
+SP_API int sp_flash_decode_sink(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
+                                const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
+                                int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
+                                int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats, int* counters,
+                                const float* sink, cudaStream_t stream) {
+    return sp_flash_decode_bias(q, out, out_dt, kpool, vpool, seq_len, seq_row, page_table, max_pages, page_size, n_seqs, nh,
+                                nkv, hd, window, scale, chunk_tiles, n_chunks, scratch, scratch_floats, counters, sink, nullptr, 0,
+                                stream);
 }
 
 SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,

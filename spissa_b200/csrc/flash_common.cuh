@@ -68,7 +68,7 @@ template <int HD, int NT, bool MASKED>
 __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, uint32_t v_tile,
                                            int key0, int tile_pos0, const int (&lo)[2], const int (&hi)[2],
                                            float scale_log2, float (&o)[HD / 8][4], float (&m)[2], float (&l)[2],
-                                           int lane) {
+                                           int lane, const float* __restrict__ bias_row = nullptr, int bias_cap = 0) {
     using T = Tile<HD>;
     float s[NT][4];
 #pragma unroll
@@ -104,8 +104,22 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[i][e] += s2[i][e];
     }
-    // mask, running maximum (of the raw scores; the scale is positive)
+    // a score by distance (``bias_row``: this head's table, natural-log units): the scores move into the log2 domain
+    // here, bias included, and the scale that the rest of the step applies is one
     const int t = lane & 3;
+    if (bias_row) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = tile_pos0 + key0 + nt * 8 + 2 * t + (e & 1);
+                const int dist = min(max(hi[e >> 1] - key, 0), bias_cap);
+                s[nt][e] = fmaf(s[nt][e], scale_log2, __ldg(bias_row + dist) * LOG2E);
+            }
+        }
+        scale_log2 = 1.0f;
+    }
+    // mask, running maximum (of the raw scores; the scale is positive)
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -186,7 +200,8 @@ template <int HD, int NH, bool MASKED>
 __device__ __forceinline__ void decode_step_t(const uint32_t (&qb)[HD / 16][NH][2], uint32_t k_tile, uint32_t v_tile,
                                               int key0, int tile_pos0, int lo, int hi, float scale_log2,
                                               float (&o)[HD / 16][NH][4], float (&m)[NH][2], float (&l)[NH][2],
-                                              int lane) {
+                                              int lane, const float* __restrict__ bias_group = nullptr, int bias_cap = 0,
+                                              int group_heads = 0) {
     using T = Tile<HD>;
     const int g = lane >> 2;
     float s[NH][4], s2[NH][4];                        // two chains of products: an mma need not wait for the one before
@@ -210,6 +225,12 @@ __device__ __forceinline__ void decode_step_t(const uint32_t (&qb)[HD / 16][NH][
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             float v = (s[i][e] + s2[i][e]) * scale_log2;
+            if (bias_group) {
+                // ``bias_group``: the table rows of this kv head's query heads, one after another; hi is the query's position
+                const int head = i * 8 + 2 * (lane & 3) + (e & 1);
+                const int dist = min(max(hi - (tile_pos0 + key0 + g + ((e >> 1) << 3)), 0), bias_cap);
+                if (head < group_heads) v += __ldg(bias_group + (size_t)head * (bias_cap + 1) + dist) * LOG2E;
+            }
             if (MASKED) {
                 const int key = tile_pos0 + key0 + g + ((e >> 1) << 3);
                 if (key > hi || key < lo) v = -INFINITY;
@@ -277,6 +298,8 @@ struct PagedKV {
     int nkv;
     SpRange rg;                 // what the debug build checks table entries against
     const float* sink = nullptr;   // [query heads] or null: per head a score that joins the softmax's denominator once, with no key and no value
+    const float* dist_bias = nullptr;   // [query heads][dist_cap + 1] or null: a score added by the distance between query and
+    int dist_cap = 0;                   // key (distances beyond dist_cap take the last entry); the scale does not multiply it
 };
 
 }  // namespace

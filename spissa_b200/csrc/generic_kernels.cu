@@ -357,6 +357,7 @@ SP_API int sp_gemm_generic(const void* A, int a_dt, const void* W, int w_dt, voi
 
 #define AG_WARPS 4
 #define AG_MAX_HD 256          // largest head size of the generic kernels
+#define AG_WIDE_HD 1024        // largest key/value row of the generic attention's wide instance
 
 // ============================================================== rope + cache write
 // qkv row t = [q heads | k heads | v heads]. Rotates q and k (rotate-half over the
@@ -610,12 +611,13 @@ __device__ __forceinline__ float ag_dot(const float* __restrict__ qv, const __nv
 
 // SPLIT: the CTA's warps share ONE (token, head) and take the chunks of 32 keys in turn (few pairs, many keys: a
 // decode step); their partial results are merged in warp order through shared memory.
-template <typename TQ, typename TC, bool SPLIT>
+// MAXD: the largest key or value size this instance holds (256, or AG_WIDE_HD for rows of a cached low-rank latent)
+template <typename TQ, typename TC, bool SPLIT, int MAXD>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
                          TQ* __restrict__ out, KvPlace pl, int T, int nh, int nkv, int hd, int vd, int window,
                          float scale, const float* __restrict__ sink, const float* __restrict__ dist_bias, int dist_cap) {
-    __shared__ __align__(16) float qs[AG_WARPS][AG_MAX_HD];
+    __shared__ __align__(16) float qs[AG_WARPS][MAXD];
     __shared__ float part_ml[AG_WARPS][2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long gw = SPLIT ? (long long)blockIdx.x : (long long)blockIdx.x * AG_WARPS + warp;
@@ -632,9 +634,9 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     float m = -INFINITY, l = 0.0f;
-    float acc[AG_MAX_HD / 32];
+    float acc[MAXD / 32];
 #pragma unroll
-    for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < MAXD / 32; ++i) acc[i] = 0.0f;
 
     for (int j0 = lo + (SPLIT ? 32 * warp : 0); j0 <= p; j0 += SPLIT ? 32 * AG_WARPS : 32) {
         const int j = j0 + lane;
@@ -653,7 +655,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
         const float corr = expf(m - m_new);              // first chunk: exp(-inf) = 0
         l = l * corr + sp_warp_sum(e);
 #pragma unroll
-        for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] *= corr;
+        for (int i = 0; i < MAXD / 32; ++i) acc[i] *= corr;
         const int n_valid = min(32, p - j0 + 1);
         // eight keys at a time: their value rows are asked for together, then added in key order
         for (int jj0 = 0; jj0 < n_valid; jj0 += 8) {
@@ -667,7 +669,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
                 vr[u] = vpool + (((size_t)pg * nkv + g) * ps + of) * vd;
             }
 #pragma unroll
-            for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+            for (int i = 0; i < MAXD / 32; ++i) {
                 const int d = lane + 32 * i;
                 if (d < vd) {
                     float v[8];
@@ -684,7 +686,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
         // every warp leaves (m, l, acc) in shared memory (its query row is no longer needed); warp 0 merges in warp order
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+        for (int i = 0; i < MAXD / 32; ++i) {
             const int d = lane + 32 * i;
             if (d < vd) qs[warp][d] = acc[i];
         }
@@ -695,13 +697,13 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
         for (int w = 0; w < AG_WARPS; ++w) mm = fmaxf(mm, part_ml[w][0]);
         float ll = 0.0f;
 #pragma unroll
-        for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < MAXD / 32; ++i) acc[i] = 0.0f;
         for (int w = 0; w < AG_WARPS; ++w) {
             if (part_ml[w][1] <= 0.0f) continue;                 // a warp that saw no key
             const float f = expf(part_ml[w][0] - mm);
             ll += part_ml[w][1] * f;
 #pragma unroll
-            for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+            for (int i = 0; i < MAXD / 32; ++i) {
                 const int d = lane + 32 * i;
                 if (d < vd) acc[i] = fmaf(qs[w][d], f, acc[i]);
             }
@@ -716,10 +718,10 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
         const float f = expf(m - m_all);
         l = l * f + expf(sk - m_all);
 #pragma unroll
-        for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] *= f;
+        for (int i = 0; i < MAXD / 32; ++i) acc[i] *= f;
     }
 #pragma unroll
-    for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+    for (int i = 0; i < MAXD / 32; ++i) {
         const int d = lane + 32 * i;
         if (d < vd) sp_st(out, (size_t)t * nh * vd + (size_t)h * vd + d, acc[i] / l);
     }
@@ -732,8 +734,9 @@ SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, cons
                                 int dist_cap, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (dist_bias && dist_cap < 0) SP_FAIL("attention: a distance-bias table needs at least one entry per head");
-    if (hd <= 0 || hd > AG_MAX_HD) SP_FAIL("attention: head_dim %d is beyond this kernel's limit %d", hd, AG_MAX_HD);
-    if (vd <= 0 || vd > AG_MAX_HD) SP_FAIL("attention: value size %d is beyond this kernel's limit %d", vd, AG_MAX_HD);
+    if (hd <= 0 || hd > AG_WIDE_HD) SP_FAIL("attention: head_dim %d is beyond this kernel's limit %d", hd, AG_WIDE_HD);
+    if (vd <= 0 || vd > AG_WIDE_HD) SP_FAIL("attention: value size %d is beyond this kernel's limit %d", vd, AG_WIDE_HD);
+    const bool wide = hd > AG_MAX_HD || vd > AG_MAX_HD;
     if (nkv <= 0 || nh % nkv) SP_FAIL("attention: %d heads are no multiple of %d kv heads", nh, nkv);
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
     const long long warps = (long long)T * nh;
@@ -741,18 +744,20 @@ SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, cons
     const bool split = warps <= 4096;
     const long long blocks = split ? warps : (warps + AG_WARPS - 1) / AG_WARPS;
     if (blocks > 2147483647LL) SP_FAIL("attention: too many (token, head) pairs for one launch");
+#define AG_ARGS(TQ, TC) (const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink, dist_bias, dist_cap
 #define AG_LAUNCH(TQ, TC)                                                                                              \
     do {                                                                                                               \
-        if (split)                                                                                                     \
-            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink, dist_bias, dist_cap); \
-        else                                                                                                           \
-            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale, sink, dist_bias, dist_cap); \
+        if (split && wide) attention_generic_kernel<TQ, TC, true, AG_WIDE_HD><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>(AG_ARGS(TQ, TC)); \
+        else if (split) attention_generic_kernel<TQ, TC, true, AG_MAX_HD><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>(AG_ARGS(TQ, TC)); \
+        else if (wide) attention_generic_kernel<TQ, TC, false, AG_WIDE_HD><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>(AG_ARGS(TQ, TC)); \
+        else attention_generic_kernel<TQ, TC, false, AG_MAX_HD><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>(AG_ARGS(TQ, TC)); \
     } while (0)
     if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) AG_LAUNCH(float, float);
     else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) AG_LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) AG_LAUNCH(float, __nv_bfloat16);
     else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_F32) AG_LAUNCH(__nv_bfloat16, float);
     else SP_FAIL("attention: unsupported dtype codes %d/%d", q_dt, cache_dt);
+#undef AG_ARGS
 #undef AG_LAUNCH
     SP_CHECK_LAUNCH("attention_generic");
     return 0;

@@ -176,7 +176,7 @@ def rope_kv_write(qkv, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd, rd, w
         c_void_p(_ptr(inv_freq)), T, nh, nkv, hd, rd, int(bool(write_kv)), c_void_p(_stream())))
 
 
-FLASH_DISTANCE_BIAS = False      # whether the tensor-core attention kernels take a table of scores by distance
+FLASH_DISTANCE_BIAS = True       # whether the tensor-core attention kernels take a table of scores by distance
 
 
 def _dist_bias_args(dist_bias, nh):
@@ -587,9 +587,11 @@ def _sink_ptr(sink, nh):
     return c_void_p(_ptr(sink))
 
 
-def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, sink=None):
+def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, sink=None,
+                  dist_bias=None):
     """Causal attention of a step's tokens (any number per sequence) over the paged cache. ``sink`` (float32 [nh]):
-    per head a score that joins the softmax's denominator once and has no value.
+    per head a score that joins the softmax's denominator once and has no value. ``dist_bias`` (float32 [nh, entries]): a
+    score added by the distance between query and key, beyond the scale.
 
     ``seq_start`` [B+1] int32 on the device; ``n_q_tiles`` = sum over sequences of ceil(new tokens /
     ``flash_query_tile()``).
@@ -598,11 +600,12 @@ def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh
     _need_contig(q, out)
     pt = meta.page_table
     _declare_bounds("attention", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
-    _check("attention", lib.sp_flash_prefill_sink(
+    bias_ptr, bias_cap = _dist_bias_args(dist_bias, nh)
+    _check("attention", lib.sp_flash_prefill_bias(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)),
         c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles), nh, nkv, hd,
-        int(window or 0), c_float(scale), _sink_ptr(sink, nh), c_void_p(_stream())))
+        int(window or 0), c_float(scale), _sink_ptr(sink, nh), bias_ptr, bias_cap, c_void_p(_stream())))
 
 
 def flash_decode_plan(n_seqs: int, nkv: int, max_len: int, page_size: int = 64) -> tuple:
@@ -628,7 +631,7 @@ def flash_decode_scratch_floats(n_seqs: int, nh: int, hd: int, n_chunks: int) ->
 
 
 def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, scale, chunk_tiles, n_chunks, scratch,
-                 counters=None, sink=None):
+                 counters=None, sink=None, dist_bias=None):
     """One query token per sequence: keys split into chunks over CTAs, partial results combined in order.
 
     ``seq_len`` [B] int32: each sequence's length including the query token. ``scratch``: float32,
@@ -643,12 +646,13 @@ def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, sca
     if counters is not None and (counters.dtype != torch.int32 or counters.numel() < n_seqs * nkv):
         raise KernelError("flash_decode: counters must be int32 with a word per (sequence, kv head)")
     _declare_bounds("attention", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
-    _check("attention", lib.sp_flash_decode_sink(
+    bias_ptr, bias_cap = _dist_bias_args(dist_bias, nh)
+    _check("attention", lib.sp_flash_decode_bias(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_void_p(_ptr(seq_len)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
         n_seqs, nh, nkv, hd, int(window or 0), c_float(scale), int(chunk_tiles), int(n_chunks),
         c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_ptr(counters)), _sink_ptr(sink, nh),
-        c_void_p(_stream())))
+        bias_ptr, bias_cap, c_void_p(_stream())))
     if counters is None:
         launches += 1        # two kernels: the chunks and the combine
 
