@@ -5,6 +5,7 @@
     python bench.py --design duzinex [--design-sizes 1k,2k,4k]      (the Duzinex decoder beside Llama at equal sizes)
     python bench.py --design gozatar [--design-sizes 1k,2k,4k]      (the Gozatar decoder likewise)
     python bench.py --design kugirax [--design-sizes 1k,2k,4k]      (the Kugirax decoder likewise)
+    python bench.py --design fotulix [--design-sizes 1k,2k,4k]      (the Fotulix decoder beside Kugirax and Llama)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 from prompts of
 about 2,048 tokens in a cache of 4,096 tokens per sequence, timed on the device with CUDA
@@ -263,6 +264,60 @@ def kugirax_config(size: dict, kx: dict, window: int = DESIGN_WINDOW) -> dict:
     return dict(architecture="Kugirax", vocab=DESIGN_VOCAB, width=W, norm=dict(eps=1e-6), logit_softcap=30.0, layers=layers)
 
 
+# --design fotulix: eight layers, every sublayer between two norms, a pair table and a token side input of 256; layers 0
+# and 4 an attention through cached rows (rank + 64 rotated dims shared by the heads, window 1,024), layer 4 reading the
+# rows layer 0 cached; layers 2 and 6 a grouped-query attention with half of each head rotated and a sink; the other four
+# a grouped-query attention with biases, a query factor and a table of 32 scores by distance. Dense feed-forwards of
+# ``ff``. Beside it the closest existing design at equal sizes: a Kugirax decoder of eight layers with its latent
+# attention at the same two places (rows of the same size, the same window) and dense feed-forwards, and Llama.
+FOTULIX_SIZES = {
+    # (attention: heads, kv heads, dim), (latent: heads, dim, rot_dim, vdim, kv_rank), Kugirax's query rank
+    "1k": dict(att=(8, 2, 128), lat=(8, 128, 64, 128, 192), q_rank=512),
+    "2k": dict(att=(16, 4, 128), lat=(16, 128, 64, 128, 192), q_rank=768),
+    "4k": dict(att=(32, 8, 128), lat=(32, 128, 64, 128, 448), q_rank=1536),
+}
+FOTULIX_LAYERS, FOTULIX_LATENT, FOTULIX_SINK = 8, (0, 4), (2, 6)
+FOTULIX_SIDE = 256
+
+
+def fotulix_config(size: dict, fx: dict, window: int = DESIGN_WINDOW) -> dict:
+    W, ff = size["width"], size["ff"]
+    h, g, d = fx["att"]
+    lh, ld, lrd, lvd, r = fx["lat"]
+    biased = dict(heads=h, kv_heads=g, dim=d, vdim=d, scale=d ** -0.5, q_temp=dict(coef=0.2, every=512), bias_max=4096, bias_rows=32)
+    turned = dict(heads=h, kv_heads=g, dim=d, vdim=d, scale=d ** -0.5,
+                  rot=dict(dims=d // 2, base=500000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    lat = dict(heads=lh, dim=ld, rot_dim=lrd, vdim=lvd, kv_rank=r, scale=(ld + lrd) ** -0.5, mask=dict(size=window),
+               rot=dict(dims=lrd, base=10000.0, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
+    layers = []
+    for i in range(FOTULIX_LAYERS):
+        if i in FOTULIX_LATENT:
+            m = dict(lat, kv_from=FOTULIX_LATENT[0]) if i != FOTULIX_LATENT[0] else lat
+            layers.append(dict(type="latent_attention", mixer=m, mlp=dict(kind="dense", ff=ff)))
+        else:
+            layers.append(dict(type="attention_2" if i in FOTULIX_SINK else "attention", mixer=turned if i in FOTULIX_SINK else biased,
+                               mlp=dict(kind="dense", ff=ff)))
+    return dict(architecture="Fotulix", vocab=DESIGN_VOCAB, width=W, norm=dict(eps=1e-6), residual_mult=0.5,
+                embedding=dict(scale=W ** 0.5, bigram=dict(buckets=65521, mul_prev=127, mul_cur=7)),
+                token_side=dict(dim=FOTULIX_SIDE), layers=layers)
+
+
+def kugirax_config_like_fotulix(size: dict, fx: dict, window: int = DESIGN_WINDOW) -> dict:
+    W, ff = size["width"], size["ff"]
+    h, g, d = fx["att"]
+    lh, ld, lrd, lvd, r = fx["lat"]
+    att = dict(heads=h, kv_heads=g, dim=d, vdim=d, conv=4, scale=d ** -0.5, rot=dict(dims=d, base=10000.0))
+    lat = dict(heads=lh, dim=ld, vdim=lvd, q_rank=fx["q_rank"], kv_rank=r + lrd, scale=ld ** -0.5, mask=dict(size=window))
+    layers = []
+    for i in range(FOTULIX_LAYERS):
+        if i in FOTULIX_LATENT:
+            m = dict(lat, kv_from=FOTULIX_LATENT[0]) if i != FOTULIX_LATENT[0] else lat
+            layers.append(dict(type="latent_attention", mixer=m, mlp=dict(kind="dense", ff=ff)))
+        else:
+            layers.append(dict(type="attention", mixer=att, mlp=dict(kind="dense", ff=ff)))
+    return dict(architecture="Kugirax", vocab=DESIGN_VOCAB, width=W, norm=dict(eps=1e-6), logit_softcap=30.0, layers=layers)
+
+
 def design_compare(args) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8 behind such prompts) of the Duzinex decoder and of the
     Llama decoder with the same width, feed-forward size and number of layer runs; per-phase device times of both
@@ -282,10 +337,14 @@ def design_compare(args) -> int:
     for name in names:
         size = DESIGN_SIZES[name]
         dz = (duzinex_config(size) if design == "duzinex" else gozatar_config(size, GOZATAR_SIZES[name]) if design == "gozatar"
-              else kugirax_config(size, KUGIRAX_SIZES[name]))
+              else kugirax_config(size, KUGIRAX_SIZES[name]) if design == "kugirax" else fotulix_config(size, FOTULIX_SIZES[name]))
         runs = len(config_from_dict(dz).to_spec().schedule)
         row = {}
-        for label, cfg_dict in ((design, dz), ("llama", llama_config_like(size, runs))):
+        arms = [(design, dz), ("llama", llama_config_like(size, runs))]
+        if design == "fotulix":
+            arms.insert(1, ("kugirax", kugirax_config_like_fotulix(size, FOTULIX_SIZES[name])))
+            out["beside"] = "kugirax, llama"
+        for label, cfg_dict in arms:
             cfg = config_from_dict(cfg_dict)
             engine = Engine.from_config(cfg, seed=0, dtype=args.dtype, max_tokens=B * (T + 128), max_seqs=B, device="cuda:0")
             rng = random.Random(7)
@@ -358,7 +417,8 @@ def design_compare(args) -> int:
         eb = 4 if args.dtype == "float32" else 2
         row["rooflines"] = (design_rooflines(size, row, T, B, peaks, eb) if design == "duzinex"
                             else gozatar_rooflines(size, GOZATAR_SIZES[name], row, T, peaks, eb) if design == "gozatar"
-                            else kugirax_rooflines(size, KUGIRAX_SIZES[name], row, T, peaks, eb))
+                            else kugirax_rooflines(size, KUGIRAX_SIZES[name], row, T, peaks, eb) if design == "kugirax"
+                            else fotulix_rooflines(size, FOTULIX_SIZES[name], row, T, B, peaks, eb))
         out["sizes"][name] = row
     print(json.dumps(out))
     return 0
@@ -488,6 +548,77 @@ def kugirax_rooflines(size, kx, row, T, peaks, eb) -> dict:
     out["norm (hbm)"] = dict(ms=kz.get("input_norm_ms"), frac=frac(KUGIRAX_LAYERS * T * W * (4.0 + eb), bw, kz.get("input_norm_ms")))
     # Llama's norms ride in the products' prologues but for the first layer's: one launch
     out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    return out
+
+
+def fotulix_rooflines(size, fx, row, T, B, peaks, eb) -> dict:
+    """The same for the Fotulix decoder's kernel groups of a prompt step (sums over its eight layers), beside the like
+    groups of the Kugirax decoder at equal sizes and of Llama."""
+    W, ff = size["width"], size["ff"]
+    h, g, d = fx["att"]
+    lh, ld, lrd, lvd, r = fx["lat"]
+    nh, nkv, hd = size["llama"]
+    fz, kz, ll = row["fotulix"]["prefill_phases_ms"], row["kugirax"]["prefill_phases_ms"], row["llama"]["prefill_phases_ms"]
+    tf, bw = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    L, n_lat, n_sink = FOTULIX_LAYERS, len(FOTULIX_LATENT), len(FOTULIX_SINK)
+    n_bias = L - n_lat - n_sink
+    win = min(T, DESIGN_WINDOW)
+    pairs = T * win - win * (win - 1) / 2
+    causal = T * (T + 1) / 2
+    R = r + lrd
+    frac = lambda work, peak, ms: round(work / (ms * 1e-3) / peak, 4) if ms else None
+    out = {}
+    out["attention with scores by distance (tensor)"] = dict(ms=fz.get("distance_attention_ms"),
+                                                             frac=frac(n_bias * 4.0 * causal * d * h, tf, fz.get("distance_attention_ms")))
+    out["attention with a sink (tensor)"] = dict(ms=fz.get("attention_ms"), frac=frac(n_sink * 4.0 * causal * d * h, tf, fz.get("attention_ms")))
+    out["kugirax attention (tensor)"] = dict(ms=kz.get("attention_ms"), frac=frac((L - n_lat) * 4.0 * causal * d * h, tf, kz.get("attention_ms")))
+    ll_att, ll_runs = ll.get("attention_ms"), row["llama"]["layer_runs"]
+    out["llama attention (tensor)"] = dict(ms=ll_att, frac=frac(ll_runs * 4.0 * causal * hd * nh, tf, ll_att))
+    # per (query, visible key) pair and head 2·(dim + rot_dim) FLOPs for the score and 2·vdim for the weighted sum: the
+    # least any form does (over the cached rows themselves it is 4·(rank + rot_dim))
+    lat_ms = (fz.get("latent_attention_ms") or 0) + (fz.get("key_value_expansion_ms") or 0)
+    out["latent attention (tensor)"] = dict(ms=lat_ms, frac=frac(n_lat * 2.0 * pairs * (ld + lrd + lvd) * lh, tf, lat_ms))
+    k_lat = (kz.get("latent_attention_ms") or 0) + (kz.get("key_value_expansion_ms") or 0)
+    out["kugirax latent attention (tensor)"] = dict(ms=k_lat, frac=frac(n_lat * 2.0 * pairs * (ld + lvd) * lh, tf, k_lat))
+    hp = (fz.get("query_into_latent_space_ms") or 0) + (fz.get("value_expansion_ms") or 0)
+    if hp:
+        out["per-head products (tensor)"] = dict(ms=hp, frac=frac(n_lat * T * lh * 2.0 * R * (ld + lrd + lvd), tf, hp))
+    k_hp = (kz.get("query_into_latent_space_ms") or 0) + (kz.get("value_expansion_ms") or 0)
+    if k_hp:
+        out["kugirax per-head products (tensor)"] = dict(ms=k_hp, frac=frac(n_lat * T * lh * 2.0 * R * (ld + lvd), tf, k_hp))
+    C = (h + g) * d + g * d
+    out["bias+factor+rotation+store (hbm)"] = dict(ms=fz.get("rotary+kv_append_ms"),
+                                                   frac=frac((L - n_lat) * T * ((C + h) * 4.0 + C * eb + h * 4.0), bw, fz.get("rotary+kv_append_ms")))
+    k_store = kz.get("conv+rotary+kv_append_ms")
+    out["kugirax conv+rotary+store (hbm)"] = dict(ms=k_store, frac=frac((L - n_lat) * T * ((h + g) * d * 4.0 + (h + 2 * g) * d * eb), bw, k_store))
+    q_w = lh * (ld + lrd)
+    out["row norm+rotation+store (hbm)"] = dict(ms=fz.get("latent_norm+rotary+append_ms"),
+                                                frac=frac(T * ((2 * q_w + R + 2 * lh) * 4.0 + (2 * q_w + R) * eb + 2 * lh * 4.0), bw,
+                                                          fz.get("latent_norm+rotary+append_ms")))
+    out["kugirax latent norms+append (hbm)"] = dict(ms=kz.get("latent_norm+append_ms"),
+                                                    frac=frac(T * (2 * fx["q_rank"] + R) * (4.0 + eb), bw, kz.get("latent_norm+append_ms")))
+    # three passes per layer: the stream and the sublayer's sum read, both written (the sum as zeros), two of them also
+    # write the next reader's input
+    post = (fz.get("attention_out_norm+mlp_norm_ms") or 0) + (fz.get("out_norm_ms") or 0) + (fz.get("side_out_norm_ms") or 0)
+    out["norms into the stream (hbm)"] = dict(ms=post, frac=frac(L * T * W * (3 * 4 * 4.0 + 2 * eb), bw, post))
+    out["norm (hbm)"] = dict(ms=fz.get("attention_norm_ms"), frac=frac(L * T * W * (4.0 + eb), bw, fz.get("attention_norm_ms")))
+    out["kugirax norm (hbm)"] = dict(ms=kz.get("input_norm_ms"), frac=frac(L * T * W * (4.0 + eb), bw, kz.get("input_norm_ms")))
+    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    out["head gates (hbm)"] = dict(ms=fz.get("head_gate_ms"), frac=frac(T * ((L - n_lat) * h * d + n_lat * lh * lvd) * 2 * eb, bw, fz.get("head_gate_ms")))
+    side = (fz.get("side_gate_ms") or 0) + (fz.get("side_projection_ms") or 0)
+    out["token side input (hbm)"] = dict(ms=side, frac=frac(L * T * (W * eb + 3 * FOTULIX_SIDE * eb + W * 4.0 * 2), bw, side))
+    f_ff = sum(v for k, v in fz.items() if "gate_projection" in k or "down_projection" in k)
+    k_ff = sum(v for k, v in kz.items() if "gate_projection" in k or "down_projection" in k)
+    ll_ff = sum(v for k, v in ll.items() if "gate_projection" in k or "down_projection" in k)
+    out["feed-forward (tensor)"] = dict(ms=f_ff, frac=frac(L * T * 3 * 2.0 * W * ff, tf, f_ff))
+    out["kugirax feed-forward (tensor)"] = dict(ms=k_ff, frac=frac(L * T * 3 * 2.0 * W * ff, tf, k_ff))
+    out["llama feed-forward (tensor)"] = dict(ms=ll_ff, frac=frac(ll_runs * T * 3 * 2.0 * W * ff, tf, ll_ff))
+    # a decode step streams every weight once and, per sequence, the cached keys and values (windowed rows: the window's)
+    for label, kv_bytes in (("fotulix", B * T * (L - n_lat) * 2 * g * d * eb + B * win * R * eb),
+                            ("kugirax", B * T * (L - n_lat) * 2 * g * d * eb + B * win * R * eb),
+                            ("llama", B * T * ll_runs * 2 * nkv * hd * eb)):
+        ms = row[label]["decode_ms_per_step"]
+        out[f"{label} decode step (hbm)"] = dict(ms=ms, frac=frac(row[label]["weight_gb"] * 1e9 + kv_bytes, bw, ms))
     return out
 
 
@@ -972,7 +1103,7 @@ def main() -> int:
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
                          "gemv_down|gemv_head|diff_flash|diff_decode|retention_chunks|retention_step|mingru_chunks|polynorm|token_shift|gla_chunks|gla_step|moe_experts|moe_experts_b8|streams_norm|conv_qk_store|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
-    ap.add_argument("--design", default=None, choices=["duzinex", "gozatar", "kugirax"],
+    ap.add_argument("--design", default=None, choices=["duzinex", "gozatar", "kugirax", "fotulix"],
                     help="measure this design beside the Llama decoder at equal layer sizes instead of the headline workload")
     ap.add_argument("--design-sizes", default="", dest="design_sizes", help="which of 1k,2k,4k (default: all)")
     ap.add_argument("--reps", type=int, default=20)

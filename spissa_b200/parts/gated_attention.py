@@ -142,7 +142,7 @@ class GatedAttention(Mixer):
             coef, every = self.q_temp or (0.0, 1)
             K.gated_qkv_store(proj, self.qkv_bias, q, cache.k_pool, cache.v_pool, cache, gates, freq, nh, g, d, vd, rd,
                               write_kv=cache.writes, rot_mult=amp, temp_coef=coef, temp_every=every)
-        with phase("attention_ms"):
+        with phase("distance_attention_ms" if self.dist is not None else "attention_ms"):
             ctx = self.attend(q, step, cache)
         with phase("head_gate_ms"):
             K.scale_rows_sigmoid(ctx.view(T * nh, vd), gates.view(T * nh))

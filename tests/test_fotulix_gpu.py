@@ -1,0 +1,704 @@
+"""The Fotulix parts and the whole decoder against the plain implementation in ``plain/fotulix_plain.py``.
+
+Each mechanism alone (kernel against its formula: the pair embedding with its word of state, a sublayer's norm into the
+stream, the gathered gate of the token side input, biases with the query factor and the rotation of neighbouring
+pairs, the low-rank row with its shared rotated key part in one page row, scores by distance and sinks on every kernel
+that can serve them, unequal key and value sizes), then small models with random weights under every way of cutting
+the work: whole prompts, token-by-token decoding, portions down to two tokens, batches of unequal requests, slots and
+pages used again, long decoding with windows that pass over decoded tokens, greedy generation through
+``Engine.generate``, the trace program and the command line. Where random weights would hide a fault (one key among
+many, a window's edge, a sink, a row of the distance table), the weights or inputs are made so that it shows.
+"""
+import json
+import math
+import os
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import fotulix_models as M
+import tiny
+import traces
+from plain import fotulix_plain as P
+from spissa_b200 import Engine, SamplingParams
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PAGE = 64
+# the largest difference of a logits row, as a share of the largest logit; in bfloat16 every sublayer's rounding passes a
+# norm that keeps its relative size, so the rows' mean difference is bounded as well as the worst
+TOL = {"float32": 2e-5, "bfloat16": 5e-2}
+# Whole models with random weights, several layers deep: every sublayer's output passes a norm and enters the stream at
+# a fixed share, so its bfloat16 rounding does too (a pre-norm model's sublayers add little to a large stream at random
+# weights; here each adds about half the stream's size). The worst of hundreds of rows lies well above the mean; a fault
+# of a mechanism (the 32-bit runs bound those at 2e-5) moves single rows by the size of the logits.
+DEEP_TOL = {"float32": 2e-5, "bfloat16": 1e-1}
+MEAN_TOL = {2e-5: 2e-5, 5e-2: 1e-2, 1e-1: 2e-2}
+
+
+def i32(v):
+    return torch.tensor(v, dtype=torch.int32, device=DEV)
+
+
+def worst(got, ref):
+    return float((got.double().cpu() - ref.double()).abs().max() / ref.abs().max())
+
+
+def compare(got, ref, tol, what):
+    assert set(got) == set(ref), what
+    scale = max(float(v.abs().max()) for v in ref.values())
+    errs = [(float((row.double() - ref[k].double()).abs().max()) / scale, k) for k, row in got.items()]
+    assert all(e == e for e, _ in errs), what
+    e, k = max(errs, key=lambda x: x[0])
+    assert e <= tol, f"{what}: the worst row is {e:.3e} of the largest logit away, at {k}"
+    mean = sum(x for x, _ in errs) / len(errs)
+    assert mean <= MEAN_TOL.get(tol, tol), f"{what}: the rows are {mean:.3e} of the largest logit away on average"
+
+
+class Paged:
+    """Sequences in scattered pages, fed in steps: the arrays a kernel wants of each step."""
+
+    def __init__(self, pages, n_pages, heads, dim, dtype=torch.float32, vdim=None):
+        self.pages, self.at = pages, [0] * len(pages)
+        width = max(len(p) for p in pages)
+        table = torch.zeros(len(pages) + 1, width, dtype=torch.int32)
+        for b, p in enumerate(pages):
+            table[b + 1, :len(p)] = torch.tensor(p)                  # row 0 of the table belongs to nobody
+        self.table = table.to(DEV)
+        self.k_pool = torch.zeros(n_pages, heads, PAGE, dim, dtype=dtype, device=DEV)
+        self.v_pool = torch.zeros(n_pages, heads, PAGE, vdim, dtype=dtype, device=DEV) if vdim else self.k_pool
+
+    def step(self, counts, tokens=None):
+        """``counts[b]`` new tokens of sequence b (0: it sits this step out) -> (step, view, live sequences)."""
+        live = [b for b, n in enumerate(counts) if n > 0]
+        ns = [counts[b] for b in live]
+        starts = [0]
+        for n in ns:
+            starts.append(starts[-1] + n)
+        seq = [i for i, n in enumerate(ns) for _ in range(n)]
+        pos = [self.at[b] + t for b, n in zip(live, ns) for t in range(n)]
+        for b, n in zip(live, ns):
+            self.at[b] += n
+        lens = [self.at[b] for b in live]
+        slots = i32([b + 1 for b in live])
+        step = SimpleNamespace(seq_start=i32(starts), seq_slot=slots, token_seq=i32(seq), positions=i32(pos),
+                               n_seqs=len(live), all_single=all(n == 1 for n in ns), max_new=max(ns), max_len=max(lens),
+                               seq_len=i32(lens), host=dict(new_counts=list(ns)), tokens=i32(tokens) if tokens is not None else None)
+        view = SimpleNamespace(k_pool=self.k_pool, v_pool=self.v_pool, page_table=self.table, page_size=PAGE,
+                               token_seq=step.token_seq, positions=step.positions, seq_slot=slots, window=None, writes=True)
+        return step, view, live
+
+    def rows(self, b, n, pool=None):
+        pool = self.k_pool if pool is None else pool
+        return torch.cat([pool[p].permute(1, 0, 2) for p in self.pages[b]])[:n].cpu()
+
+
+CUTS = [[5, 1, 1, 63, 0], [2, 1, 1, 5, 0], [64, 1, 1, 1, 64]]      # three sequences of 70, 9 and 131 tokens in five steps
+LENGTHS3 = [70, 9, 131]
+PAGES3 = [[7, 3], [5], [1, 9, 4]]
+
+
+# ---------------------------------------------------------------------------------------------- each mechanism alone
+@pytest.mark.parametrize("buckets,mp,mc,W,dtype", [(37, 5, 3, 64, torch.float32), (1, 7, 11, 50, torch.float32),
+                                                   (61, 1, 1, 96, torch.bfloat16), (500, 127, 7, 33, torch.float32)])
+def test_pair_embedding_keeps_the_token_before_the_step(buckets, mp, mc, W, dtype):
+    """A sequence's first token takes the table's last row; a step that starts mid-sequence pairs its first token with
+    the last one of the step before, which the slot's word of state holds; a slot used again starts as a first token."""
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(buckets + W)
+    V, scale = 90, 3.5
+    table, pairs = torch.randn(V, W, generator=g).to(dtype), torch.randn(buckets + 1, W, generator=g).to(dtype)
+    w = {"embed": table.double(), "bigram": pairs.double()}
+    emb = dict(scale=scale, bigram=dict(buckets=buckets, mul_prev=mp, mul_cur=mc))
+    state = torch.full((5,), 77, dtype=torch.int32, device=DEV)       # what an earlier user of the slots left
+    for turn in range(2):
+        ids = [torch.randint(0, V, (n,), generator=g).tolist() for n in LENGTHS3]
+        world = Paged(PAGES3, 12, 1, 4)
+        got = [[], [], []]
+        for s in range(5):
+            at = list(world.at)
+            counts = [c[s] for c in CUTS]
+            toks = [t for b, n in enumerate(counts) for t in ids[b][at[b]:at[b] + n]]
+            step, view, live = world.step(counts, toks)
+            out = torch.empty(len(toks), W, dtype=torch.float32, device=DEV)
+            K.pair_embed(table.to(DEV), pairs.to(DEV), step, state, out, buckets, mp, mc, scale, K.status_word(torch.device(DEV)))
+            o = 0
+            for b in live:
+                got[b].append(out[o:o + counts[b]].cpu())
+                o += counts[b]
+        for b in range(3):
+            assert worst(torch.cat(got[b]), P.embed(ids[b], w, emb)) <= 1e-6, (turn, b)
+            assert int(state[b + 1]) == ids[b][-1]
+    assert int(state[0]) == 77 and int(state[4]) == 77                # nobody's slots are left alone
+
+
+@pytest.mark.parametrize("W,dtype", [(64, torch.float32), (50, torch.float32), (192, torch.bfloat16), (1030, torch.bfloat16)])
+def test_a_sublayers_norm_into_the_stream(W, dtype):
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(W)
+    T, eps, mult = 37, 1e-3, 0.5
+    x, y = torch.randn(T, W, generator=g), 3 * torch.randn(T, W, generator=g) + 0.5
+    w_post, w_next = 1 + 0.3 * torch.randn(W, generator=g), 1 + 0.3 * torch.randn(W, generator=g)
+    new = x.double() + mult * P.rms_unit(y.double(), eps) * w_post.double()
+    tol = 2e-6 if dtype == torch.float32 else 6e-3
+    for mode in ("none", "next", "raw"):
+        xd, yd = x.to(DEV), y.to(DEV)
+        out = torch.empty(T, W, dtype=dtype, device=DEV) if mode != "none" else None
+        K.stream_norm_add(xd, yd, w_post.to(DEV), mult, eps, w_next=w_next.to(DEV) if mode == "next" else None, out=out,
+                          raw=mode == "raw")
+        assert worst(xd, new) <= 2e-6 and float(yd.abs().max()) == 0.0
+        if mode == "next":
+            assert worst(out, P.rms_unit(new, eps) * w_next.double()) <= tol
+        elif mode == "raw":
+            assert worst(out, new) <= tol
+
+
+@pytest.mark.parametrize("C,layers,dtype", [(6, 5, torch.float32), (24, 3, torch.bfloat16), (5, 1, torch.float32)])
+def test_gelu_of_the_gate_times_the_tokens_part_of_the_table(C, layers, dtype):
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(C)
+    T, V = 41, 30
+    table = torch.randn(V, layers * C, generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), generator=g)
+    z = (2 * torch.randn(T, C, generator=g)).to(dtype)
+    for i in range(layers):
+        out = torch.empty(T, C, dtype=dtype, device=DEV)
+        K.gelu_gather_mul(z.to(DEV), table.to(DEV), ids.to(DEV).int(), out, i * C)
+        ref = P.gelu_tanh(z.double()) * table.double()[ids][:, i * C:(i + 1) * C]
+        assert worst(out, ref) <= (2e-6 if dtype == torch.float32 else 8e-3), i
+
+
+@pytest.mark.parametrize("nh,nkv,d,vd,rd,temp,dtype", [(4, 2, 16, 16, 0, (0.3, 16), torch.float32), (3, 1, 10, 7, 0, (0.2, 7), torch.float32),
+                                                       (3, 3, 8, 8, 4, None, torch.float32), (8, 2, 64, 64, 32, None, torch.bfloat16),
+                                                       (2, 2, 64, 32, 64, (0.5, 1), torch.bfloat16), (1, 1, 6, 6, 2, None, torch.float32)])
+def test_biases_the_query_factor_and_the_rotation_of_neighbouring_pairs(nh, nkv, d, vd, rd, temp, dtype):
+    """Rows [q | k | v | gates] across steps of unequal portions over scattered pages: the biases are added before
+    anything else, the factor multiplies the biased query, the pairs (2i, 2i + 1) of the first ``rd`` dims turn."""
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(nh * d + rd)
+    C = nh * d + nkv * d + nkv * vd
+    u = [torch.randn(n, C + nh, generator=g) for n in LENGTHS3]
+    bias = torch.randn(C, generator=g).to(dtype) if temp else None
+    freq = torch.tensor([30.0 ** (-2.0 * i / rd) for i in range(rd // 2)], dtype=torch.float32) if rd else None
+    amp = 1.2 if rd else 1.0
+    world = Paged(PAGES3, 12, nkv, d, dtype, vdim=vd)
+    q_rows, gate_rows = [[], [], []], [[], [], []]
+    for s in range(5):
+        at = list(world.at)
+        counts = [c[s] for c in CUTS]
+        step, view, live = world.step(counts)
+        rows = torch.cat([u[b][at[b]:at[b] + counts[b]] for b in live]).to(DEV)
+        q = torch.empty(rows.shape[0], nh * d, dtype=dtype, device=DEV)
+        gates = torch.empty(rows.shape[0], nh, dtype=torch.float32, device=DEV)
+        K.gated_qkv_store(rows, bias.to(DEV) if bias is not None else None, q, world.k_pool, world.v_pool, view, gates,
+                          freq.to(DEV) if rd else None, nh, nkv, d, vd, rd, write_kv=True, rot_mult=amp,
+                          temp_coef=temp[0] if temp else 0.0, temp_every=temp[1] if temp else 1)
+        o = 0
+        for b in live:
+            q_rows[b].append(q[o:o + counts[b]].cpu())
+            gate_rows[b].append(gates[o:o + counts[b]].cpu())
+            o += counts[b]
+    tol = 3e-6 if dtype == torch.float32 else 6e-3
+    for b, n in enumerate(LENGTHS3):
+        full = u[b][:, :C].double() + (bias.double() if bias is not None else 0.0)
+        rq, rk = full[:, :nh * d].view(n, nh, d), full[:, nh * d:nh * d + nkv * d].view(n, nkv, d)
+        rv = full[:, nh * d + nkv * d:].view(n, nkv, vd)
+        if temp:
+            pos = torch.arange(n)
+            rq = rq * (1.0 + temp[0] * torch.log(torch.floor((pos + 1) / temp[1]).double() + 1.0))[:, None, None]
+        if rd:
+            rq = torch.cat([P.rotate_pairs(rq[..., :rd], freq.double(), amp), rq[..., rd:]], dim=-1)
+            rk = torch.cat([P.rotate_pairs(rk[..., :rd], freq.double(), amp), rk[..., rd:]], dim=-1)
+        assert worst(torch.cat(q_rows[b]), rq.reshape(n, -1)) <= tol, b
+        assert worst(world.rows(b, n), rk) <= tol, b
+        assert worst(world.rows(b, n, world.v_pool), rv) <= tol, b
+        assert worst(torch.cat(gate_rows[b]), u[b][:, C:].double()) <= 1e-6, b
+
+
+@pytest.mark.parametrize("H,d,rd,rank,dtype", [(3, 8, 4, 20, torch.float32), (2, 5, 6, 11, torch.float32), (8, 64, 32, 96, torch.bfloat16),
+                                               (1, 6, 2, 1, torch.float32), (5, 16, 16, 112, torch.bfloat16)])
+def test_the_low_rank_row_and_the_shared_rotated_key_part_in_one_page_row(H, d, rd, rank, dtype):
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(H * d + rank)
+    eps, amp = 1e-3, 1.1 + 0.01 * rd
+    C = H * (d + rd) + rank + rd
+    u = [2 * torch.randn(n, C + H, generator=g) + 0.3 for n in LENGTHS3]
+    wc = torch.randn(rank, generator=g).to(dtype)
+    freq = torch.tensor([100.0 ** (-2.0 * i / rd) for i in range(rd // 2)], dtype=torch.float32)
+    world = Paged(PAGES3, 12, 1, rank + rd, dtype)
+    q_rows = [[], [], []]
+    for s in range(5):
+        at = list(world.at)
+        counts = [c[s] for c in CUTS]
+        step, view, live = world.step(counts)
+        rows = torch.cat([u[b][at[b]:at[b] + counts[b]] for b in live]).to(DEV)
+        q = torch.empty(rows.shape[0], H * (d + rd), dtype=dtype, device=DEV)
+        gates = torch.empty(rows.shape[0], H, dtype=torch.float32, device=DEV)
+        K.latent_rot_store(rows, wc.to(DEV), q, world.k_pool, view, gates, freq.to(DEV), H, d, rd, rank, amp, eps)
+        o = 0
+        for b in live:
+            q_rows[b].append(q[o:o + counts[b]].cpu())
+            o += counts[b]
+            assert worst(gates[o - counts[b]:o], u[b][at[b]:at[b] + counts[b], C:].double()) <= 1e-6
+    tol = 3e-6 if dtype == torch.float32 else 6e-3
+    for b, n in enumerate(LENGTHS3):
+        x = u[b].double()
+        rq = x[:, :H * (d + rd)].view(n, H, d + rd)
+        rq = torch.cat([rq[..., :d], P.rotate_pairs(rq[..., d:], freq.double(), amp)], dim=-1)
+        low = x[:, H * (d + rd):H * (d + rd) + rank]
+        part = P.rotate_pairs(x[:, None, H * (d + rd) + rank:C], freq.double(), amp)[:, 0]
+        assert worst(torch.cat(q_rows[b]), rq.reshape(n, -1)) <= tol, b
+        assert worst(world.rows(b, n)[:, 0, :rank], P.rms_unit(low, eps) * wc.double()) <= tol, b
+        assert worst(world.rows(b, n)[:, 0, rank:], part) <= tol, b
+    # a reader of another layer's rows has no row of its own: its queries turn, no page is written
+    before = world.k_pool.clone()
+    step, view, live = Paged([[2]], 12, 1, rank + rd, dtype).step([4])
+    rows = u[0][:4, list(range(H * (d + rd))) + list(range(C, C + H))].contiguous().to(DEV)
+    q = torch.empty(4, H * (d + rd), dtype=dtype, device=DEV)
+    gates = torch.empty(4, H, dtype=torch.float32, device=DEV)
+    K.latent_rot_store(rows, None, q, None, view, gates, freq.to(DEV), H, d, rd, rank, amp, eps)
+    rq = u[0][:4, :H * (d + rd)].double().view(4, H, d + rd)
+    rq = torch.cat([rq[..., :d], P.rotate_pairs(rq[..., d:], freq.double(), amp)], dim=-1)
+    assert worst(q, rq.reshape(4, -1)) <= tol and torch.equal(before, world.k_pool)
+
+
+def _run_attention(world, q, k, v, cuts, call):
+    """Feed the sequences in steps; rows are written to their pages by hand just before the step that brings them."""
+    got = [[] for _ in q]
+    for s in range(len(cuts[0])):
+        at = list(world.at)
+        counts = [c[s] for c in cuts]
+        if not any(counts):
+            continue
+        step, view, live = world.step(counts)
+        for b in live:
+            for t in range(at[b], at[b] + counts[b]):
+                world.k_pool[world.pages[b][t // PAGE], :, t % PAGE] = k[b][t].to(DEV)
+                world.v_pool[world.pages[b][t // PAGE], :, t % PAGE] = v[b][t].to(DEV)
+        rows = torch.cat([q[b][at[b]:at[b] + counts[b]] for b in live])
+        out = call(rows.reshape(rows.shape[0], -1).to(DEV).contiguous(), step, view)
+        o = 0
+        for b in live:
+            got[b].append(out[o:o + counts[b]].cpu())
+            o += counts[b]
+    return [torch.cat(x) for x in got]
+
+
+def _biased_mix(q, k, v, scale, rel, far, sink=None, window=None):
+    """q [T, H, d], k, v [T, G, ·] of one sequence; ``rel`` [rows, H] or None."""
+    T, H = q.shape[0], q.shape[1]
+    rep = H // k.shape[1]
+    k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+    s = torch.einsum("ihd,jhd->hij", q, k) * scale
+    if rel is not None:
+        rows = torch.tensor([[P.distance_bucket(i - j, rel.shape[0], far) if j <= i else 0 for j in range(T)] for i in range(T)])
+        s = s + rel[rows].permute(2, 0, 1)
+    return P.softmax_mix(s, v, window=window, sink=sink).reshape(T, -1)
+
+
+@pytest.mark.parametrize("nh,nkv,d,vd,rows,far,sink,window", [
+    (4, 2, 16, 16, 12, 40.0, False, None), (3, 1, 10, 7, 6, 33.0, False, None), (8, 2, 64, 64, 32, 120.0, False, None),
+    (2, 2, 128, 128, 16, 64.5, True, None), (6, 3, 64, 32, 8, 300.0, True, None), (4, 1, 64, 64, 0, 0.0, True, 70),
+    (16, 1, 64, 64, 32, 250.0, False, None), (2, 1, 48, 32, 2, 5.0, True, 9), (4, 4, 128, 128, 10, 1000.0, False, 130)])
+def test_scores_by_distance_and_sinks_on_every_kernel_that_serves_them(nh, nkv, d, vd, rows, far, sink, window):
+    """The mixer's own choice of kernel (32-bit: the generic one; bfloat16: the tensor-core prompt and split-key decode
+    kernels where the sizes allow), over whole prompts, portions that start and end at page borders, and decoding. One
+    key far back stands out, and the table's entries are large, so that a wrong row or a lost key shows."""
+    from spissa_b200.parts.gated_attention import GatedAttention, distance_table
+    lengths, pages = [300, 70, 131], [[7, 3, 11, 2, 12], [5, 8], [1, 9, 4]]
+    g = torch.Generator().manual_seed(nh * d + rows)
+    rel = 1.5 * torch.randn(rows, nh, generator=g) if rows else None
+    sk = torch.linspace(-1.0, 3.0, nh) if sink else None
+    scale = 1.0 / math.sqrt(d)
+    for dtype in (torch.float32, torch.bfloat16):
+        q = [torch.randn(n, nh, d, generator=g).to(dtype) for n in lengths]
+        k = [torch.randn(n, nkv, d, generator=g).to(dtype) for n in lengths]
+        v = [torch.randn(n, nkv, vd, generator=g).to(dtype) for n in lengths]
+        q[0][:, :, 0] = 6.0
+        k[0][3] = 0.0
+        k[0][3, :, 0] = 4.0 * math.sqrt(d) / 6.0             # a score of 4 where the others are about 1
+        refs = [_biased_mix(qb.double(), kb.double(), vb.double(), scale, rel.double() if rows else None, far,
+                            sk.double() if sink else None, window) for qb, kb, vb in zip(q, k, v)]
+        part = GatedAttention(64, nh, nkv, d, vd, scale, distance_rows=rows, distance_far=far, sink=sink, window=window)
+        part.rt = SimpleNamespace(act_dtype=dtype)
+        part.dist = distance_table(rel.to(DEV), far) if rows else None
+        part.sink = sk.to(DEV) if sink else None
+        part.counters = torch.zeros(4096, dtype=torch.int32, device=DEV)
+        for cuts in ([[300], [70], [131]], [[280] + [1] * 20, [50] + [1] * 20, [111] + [1] * 20],
+                     [[2, 62, 64, 172], [3, 1, 66, 0], [64, 64, 2, 1]]):
+            world = Paged(pages, 14, nkv, d, dtype, vdim=vd if vd != d else None)
+            if vd == d:
+                world.v_pool = torch.zeros_like(world.k_pool)
+            got = _run_attention(world, q, k, v, cuts, lambda rows_, step, view: part.attend(rows_, step, view))
+            for b in range(3):
+                assert worst(got[b], refs[b]) <= (3e-6 if dtype == torch.float32 else 1.2e-2), (dtype, cuts[b][:3], b)
+    if rows:       # the table matters: a table whose rows are taken one further differs by far more than the tolerance
+        moved = _biased_mix(q[1].double(), k[1].double(), v[1].double(), scale, rel.double().roll(1, 0), far,
+                            sk.double() if sink else None, window)
+        assert worst(moved, refs[1]) > 0.05
+
+
+def test_rows_of_the_distance_table():
+    """Distances below half the rows take their own row; the last row is reached at ``far`` and kept beyond it."""
+    from spissa_b200.parts.gated_attention import distance_row, distance_table
+    for rows, far in ((32, 120.0), (12, 40.0), (6, 33.0), (2, 5.0), (9, 20.0), (16, 64.5)):
+        half = rows // 2
+        for n in range(0, 2000):
+            assert distance_row(n, rows, far) == P.distance_bucket(n, rows, far)
+        assert [distance_row(n, rows, far) for n in range(half)] == list(range(half))
+        assert distance_row(int(math.ceil(far)), rows, far) == rows - 1 and distance_row(10 ** 6, rows, far) == rows - 1
+        rel = torch.arange(rows * 3, dtype=torch.float32).view(rows, 3).to(DEV)
+        table = distance_table(rel, far).cpu()
+        assert table.shape[0] == 3 and table.shape[1] <= math.ceil(far) + 1
+        for n in range(table.shape[1]):
+            assert float(table[1, n]) == float(rel[P.distance_bucket(n, rows, far), 1])
+        assert float(table[2, -1]) == float(rel[rows - 1, 2])
+
+
+def test_frequencies_rescaled_by_bands_and_by_a_ramp():
+    from spissa_b200.parts.rope import rotary_inv_freq, rotary_amplitude
+    for dims, base, sc in ((32, 20000.0, dict(factor=4.0, low=1.0, high=4.0, original=2048)),
+                           (4, 50.0, dict(factor=4.0, low=1.0, high=4.0, original=16)),
+                           (16, 500.0, dict(factor=8.0, low=1.0, high=2.0, original=32)), (8, 100.0, None)):
+        rot = dict(dims=dims, base=base)
+        scaling = None
+        if sc:
+            rot["scaling"] = sc
+            scaling = dict(rope_type="llama3", factor=sc["factor"], low_freq_factor=sc["low"], high_freq_factor=sc["high"],
+                           original_max_position_embeddings=sc["original"])
+        got = rotary_inv_freq(base, dims, scaling)
+        assert worst(got, P.banded_frequencies(rot)) <= 1e-6
+    for dims, base, sc in ((32, 1e6, dict(factor=8.0, original=1024, fast=32.0, slow=1.0)),
+                           (4, 100.0, dict(factor=4.0, original=16, fast=8.0, slow=1.0)),
+                           (8, 10000.0, dict(factor=2.0, original=64, fast=4.0, slow=2.0)), (6, 30.0, None)):
+        rot = dict(dims=dims, base=base)
+        scaling = None
+        if sc:
+            rot["scaling"] = sc
+            scaling = dict(sc, rope_type="ramp")
+        f, amp = P.ramped_frequencies(rot)
+        assert worst(rotary_inv_freq(base, dims, scaling), f) <= 1e-6
+        assert abs(rotary_amplitude(scaling) - amp) <= 1e-12
+
+
+# ---------------------------------------------------------------------------------------------- whole models
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, cfg in M.CONFIGS.items():
+        folder = tmp_path_factory.mktemp(f"fx_{name}")
+        pcfg, w = M.make(cfg, folder, **M.INIT[name])
+        out[name] = SimpleNamespace(folder=str(folder), cfg=pcfg, w=w, vocab=cfg["vocab"])
+    return out
+
+
+def logits_of(m, toks):
+    return P.forward(m.cfg, m.w, toks)
+
+
+def refs_of(m, reqs):
+    return {(rid, p): row for rid, toks in reqs.items() for p, row in enumerate(logits_of(m, toks))}
+
+
+LENGTHS = {"a": [1, 2, 23, 64, 65, 150], "b": [3, 63, 129, 140, 70, 9], "c": [5, 1, 40, 100, 66, 31],
+           "d": [2, 70, 1, 33, 129, 64]}
+
+
+def test_layer_by_layer_the_residual_stream_follows_plain(models):
+    """The stream after every layer of a prompt, in 32-bit: the first layer that differs names the mechanism."""
+    for name in ("a", "d"):
+        m = models[name]
+        toks = tiny.random_prompt(m.vocab, 90, 12)
+        layers = []
+        P.forward(m.cfg, m.w, toks, layers_out=layers)
+        eng = Engine.from_folder(m.folder, dtype="float32", max_tokens=128, max_seqs=1)
+        seen = []
+        for block in eng.model.layers:
+            inner = block.forward
+
+            def run(h, step, cache, inner=inner):
+                inner(h, step, cache)
+                seen.append(h.detach().float().cpu().clone())
+            block.forward = run
+        s = eng.acquire()
+        eng.step([(s, toks, [len(toks) - 1])])
+        eng.release(s)
+        assert len(seen) == len(layers)
+        for i, (got, ref) in enumerate(zip(seen, layers)):
+            assert worst(got[:len(toks)], ref) <= 1e-5, f"{name}: layer {i} ({m.cfg['layers'][i]['type']})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+def test_every_cut_agrees_with_plain(models, name, dtype, tmp_path):
+    m = models[name]
+    reqs = {f"r{i}": tiny.random_prompt(m.vocab, n, 31 * i + n) for i, n in enumerate(LENGTHS[name])}
+    ref = refs_of(m, reqs)
+    decode = {rid: d for rid, d in zip(reqs, [0, 1, 22, 40, 3, 90])}
+    cuts = {"whole": traces.whole(reqs), "tail": traces.tail_one_by_one(reqs, 45),
+            "ragged": traces.ragged_batches(reqs, 3, decode),
+            "ragged_pairs": traces.ragged_batches(dict(reversed(list(reqs.items()))), 2, decode)}
+    results = {}
+    for cut, steps in cuts.items():
+        out = tmp_path / cut
+        traces.run_in_process(m.folder, dtype, steps, str(out))          # a cache that holds just this trace: slots and pages come back
+        results[cut] = traces.collect(steps, str(out), m.vocab)
+        compare(results[cut], ref, DEEP_TOL[dtype], f"{name}/{dtype}/{cut}")
+    for cut in ("tail", "ragged", "ragged_pairs"):
+        compare(results[cut], results["whole"], DEEP_TOL[dtype], f"{name}/{dtype}: {cut} against whole")
+
+
+@pytest.mark.parametrize("name", ["a", "c"])
+def test_portions_of_a_prompt_down_to_two_tokens(models, name):
+    m = models[name]
+    toks = tiny.random_prompt(m.vocab, 150, 77)
+    ref = logits_of(m, toks)
+    other = tiny.random_prompt(m.vocab, 80, 78)
+    ref_other = logits_of(m, other)
+    engine = Engine.from_folder(m.folder, dtype="float32", max_tokens=64 * 6, max_seqs=3)
+    for sizes in ([2, 2, 3, 57, 1, 64, 21], [64, 64, 22], [1, 1, 2, 146]):
+        s, s2 = engine.acquire(), engine.acquire()
+        at, rows, rows2 = 0, [], []
+        for n in sizes:
+            entries = [(s, toks[at:at + n], list(range(n)))]
+            lo2, hi2 = min(at, 80), min(at + n, 80)                      # the second request's portions end earlier
+            if hi2 > lo2:
+                entries.append((s2, other[lo2:hi2], list(range(hi2 - lo2))))
+            got = engine.step(entries).cpu()
+            rows.append(got[:n])
+            rows2.append(got[n:])
+            at += n
+        assert worst(torch.cat(rows), ref) <= 2e-5, sizes
+        assert worst(torch.cat(rows2), ref_other) <= 2e-5, sizes
+        engine.release(s)
+        engine.release(s2)
+    engine.cache.check()
+    assert engine.cache.slots.held_count == 0
+
+
+def test_slots_and_pages_that_are_used_again_start_clean(models):
+    """A slot's word of state (the token before the step) and its pages belong to the new sequence from its first token."""
+    m = models["a"]
+    engine = Engine.from_folder(m.folder, dtype="float32", max_tokens=64 * 3, max_seqs=2)
+    for turn in range(3):
+        reqs = [tiny.random_prompt(m.vocab, n, 5 * turn + n) for n in ((100, 30), (7, 120), (64, 65))[turn]]
+        slots = [engine.acquire() for _ in reqs]
+        got = engine.step([(s, r[:-2], [len(r) - 3]) for s, r in zip(slots, reqs)]).cpu()
+        for b, r in enumerate(reqs):
+            assert worst(got[b], logits_of(m, r[:-2])[-1]) <= 2e-5
+        for i in (2, 1):
+            got = engine.step([(s, [r[-i]], [0]) for s, r in zip(slots, reqs)]).cpu()
+        for b, r in enumerate(reqs):
+            assert worst(got[b], logits_of(m, r)[-1]) <= 2e-5
+        for s in slots:
+            engine.release(s)
+        engine.cache.check()
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_long_decoding_lets_windows_pass_over_decoded_tokens_and_returns_pages(models, name):
+    m = models[name]                             # a: windows of 9 and 70 on one cache; b: 100 and 33 on rows of 128
+    toks = tiny.random_prompt(m.vocab, 230, 3)
+    ref = logits_of(m, toks)
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine.from_folder(m.folder, dtype=dtype, max_tokens=64 * 4, max_seqs=1)
+        s = engine.acquire()
+        engine.step([(s, toks[:10], [])])
+        rows = torch.cat([engine.step([(s, [t], [0])]).cpu() for t in toks[10:]])
+        compare({("long", i): r for i, r in enumerate(rows)}, {("long", i): r for i, r in enumerate(ref[10:])}, DEEP_TOL[dtype], dtype)
+        for g in engine.cache.kv_groups.values():
+            flags = [p is not None for p in engine.cache.seqs[s].pages[g.name]]
+            assert flags[-1]
+            assert flags[0] == (g.request.window is None)           # the windowed groups gave their first pages back
+        engine.release(s)
+        engine.cache.check()
+
+
+def test_the_first_tokens_of_a_sequence(models):
+    """The first token has no token before it (the pair table's last row), its query factor is one while
+    ⌊(t + 1) / every⌋ is zero, and the first tokens' windows hold fewer rows than their size: in a prompt and when the
+    first tokens come one by one, in a slot whose last sequence left its state and rows there."""
+    for name in ("a", "b", "c"):
+        m = models[name]
+        engine = Engine.from_folder(m.folder, dtype="float32", max_tokens=64 * 2, max_seqs=1)
+        for toks in (tiny.random_prompt(m.vocab, 40, 1), tiny.random_prompt(m.vocab, 6, 2)):
+            ref = logits_of(m, toks)
+            s = engine.acquire()
+            assert worst(engine.step([(s, toks, list(range(len(toks))))]).cpu(), ref) <= 2e-5
+            engine.release(s)
+            s = engine.acquire()
+            rows = [engine.step([(s, [t], [0])]).cpu() for t in toks[:6]]
+            assert worst(torch.cat(rows), ref[:6]) <= 2e-5
+            engine.release(s)
+
+
+def test_sizes_that_the_tensor_core_kernels_take(tmp_path):
+    """Heads of 64 and 128 with equal key and value sizes and cached rows of 128 and 256 entries: in bfloat16 a prompt
+    of 300 tokens and the decode steps behind it run on the tensor-core attention kernels, with the table of scores by
+    distance and the sink inside them; in 32-bit on the generic ones. Both agree with plain."""
+    from spissa_b200.csrc import lib as K
+    cfg = M.model(128, 180, [M.layer("attention", M.biased(4, 2, 64, q_temp=(0.3, 128), far=200, rows=24), 192),
+                             M.layer("latent_attention", M.through_rows(4, 32, 32, 32, 96, 100, scaling=M.RAMP), 64),
+                             M.layer("attention_2", M.turned(2, 1, 128, rot=64, base=5000.0, scaling=(4.0, 1.0, 4.0, 64)), 128),
+                             M.layer("latent_attention", M.through_rows(2, 64, 32, 64, 96, 140, scaling=M.RAMP, kv_from=1)),
+                             M.layer("latent_attention", M.through_rows(3, 16, 64, 48, 192, 70), 64),
+                             M.layer("attention", M.biased(2, 2, 128, far=1000, rows=10))],
+                  mult=0.5, emb_scale=4.0, bigram=(101, 13, 5), side=16)
+    pcfg, w = M.make(cfg, tmp_path, seed=41, std=0.07)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    toks = tiny.random_prompt(180, 330, 8)
+    ref = logits_of(m, toks)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(str(tmp_path), dtype=dtype, max_tokens=64 * 7, max_seqs=1)
+        s = eng.acquire()
+        rows = [eng.step([(s, toks[:300], list(range(300)))]).cpu()]
+        rows += [eng.step([(s, [t], [0])]).cpu() for t in toks[300:]]
+        eng.release(s)
+        compare({("p", i): r for i, r in enumerate(torch.cat(rows))}, {("p", i): r for i, r in enumerate(ref)}, TOL[dtype], dtype)
+    assert "attention" in K.loaded_libraries() and "latent" in K.loaded_libraries()
+
+
+# ---------------------------------------------------------------------------------------------- one key that matters
+def _prompt_and_decoded(eng, toks, tail, tol, ref, what):
+    T = len(toks)
+    s = eng.acquire()
+    got = eng.step([(s, toks, [T - 2, T - 1])]).cpu()                              # in a prompt
+    assert worst(got, ref[-2:]) <= tol, (what, "prompt")
+    eng.release(s)
+    s = eng.acquire()
+    eng.step([(s, toks[:T - tail], [])])
+    for t in toks[T - tail:T - 2]:
+        eng.step([(s, [t], [])])
+    got = torch.cat([eng.step([(s, [t], [0])]) for t in toks[T - 2:]]).cpu()       # decoded, pages returned meanwhile
+    assert worst(got, ref[-2:]) <= tol, (what, "decoded")
+    eng.release(s)
+
+
+def _plain_base(T, seed):
+    return [t if t != M.NEEDLE else M.NEEDLE + 1 for t in tiny.random_prompt(64, T, seed)]
+
+
+@pytest.mark.parametrize("window,rank,rot_dim", [(20, 20, 4), (64, 20, 4), (70, 120, 8), (130, 96, 32), (1, 20, 4), (2, 120, 8)])
+def test_a_row_just_inside_and_just_outside_the_window(tmp_path, window, rank, rot_dim):
+    cfg, patch = M.rows_needle_model(window, rank=rank, rot_dim=rot_dim)
+    pcfg, w = M.make(cfg, tmp_path, seed=21, std=0.05, patch=patch)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    T = 200
+    base = _plain_base(T, 99)
+    places = sorted({T - 1 - (window - 1), T - 1 - window, T - 2 - (window - 1), 63, 64, T - 1})
+    engines = {dt: Engine.from_folder(str(tmp_path), dtype=dt, max_tokens=64 * 4, max_seqs=1) for dt in ("float32", "bfloat16")}
+    last = {}
+    for place in places:
+        toks = M.with_needle(base, place)
+        ref = logits_of(m, toks)
+        last[place] = ref[-1]
+        for dt in ("float32", "bfloat16"):
+            _prompt_and_decoded(engines[dt], toks, 40, TOL[dt], ref, (place, dt))
+    # the test can see the edge: a needle inside changes the last logits by far more than the tolerance
+    inside, outside = last[T - 1 - (window - 1)], last[T - 1 - window]
+    assert float((inside - outside).abs().max() / inside.abs().max()) > 0.2
+
+
+@pytest.mark.parametrize("writer,reader", [(70, 20), (20, 70), (130, 64), (9, 129)])
+def test_a_reader_of_another_layers_rows_keeps_its_own_window(tmp_path, writer, reader):
+    """The cache keeps rows for the wider of the two windows; each layer sees its own. Only the reader looks for the
+    needle: its edge, not the writer's, decides."""
+    cfg, patch = M.rows_needle_model(writer, reader_window=reader)
+    pcfg, w = M.make(cfg, tmp_path, seed=23, std=0.05, patch=patch)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    T = 200
+    base = _plain_base(T, 98)
+    engines = {dt: Engine.from_folder(str(tmp_path), dtype=dt, max_tokens=64 * 4, max_seqs=1) for dt in ("float32", "bfloat16")}
+    last = {}
+    for place in (T - 1 - (reader - 1), T - 1 - reader, T - 1 - (writer - 1), T - 1 - writer):
+        toks = M.with_needle(base, place)
+        ref = logits_of(m, toks)
+        last[place] = ref[-1]
+        for dt in ("float32", "bfloat16"):
+            _prompt_and_decoded(engines[dt], toks, 50, TOL[dt], ref, (place, dt))
+    inside, outside = last[T - 1 - (reader - 1)], last[T - 1 - reader]
+    assert float((inside - outside).abs().max() / inside.abs().max()) > 0.2
+
+
+@pytest.mark.parametrize("kind,dim,rot,heads,kv", [("attention", 16, 0, 2, 1), ("attention", 64, 0, 4, 2), ("attention_2", 16, 8, 2, 1),
+                                                   ("attention_2", 128, 32, 2, 2), ("attention_2", 64, 62, 6, 1)])
+def test_a_far_key_among_hundreds(tmp_path, kind, dim, rot, heads, kv):
+    cfg, patch = M.keys_needle_model(kind, dim, rot, heads, kv)
+    pcfg, w = M.make(cfg, tmp_path, seed=22, std=0.05, patch=patch)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    T = 700
+    base = _plain_base(T, 5)
+    plain_last = logits_of(m, base)[-1]
+    engines = {dt: Engine.from_folder(str(tmp_path), dtype=dt, max_tokens=64 * 11, max_seqs=1) for dt in ("float32", "bfloat16")}
+    for place in (0, 1, 64, 383, 640):
+        toks = M.with_needle(base, place)
+        ref = logits_of(m, toks)
+        assert float((ref[-1] - plain_last).abs().max() / ref[-1].abs().max()) > 0.2
+        for dt, eng in engines.items():
+            s = eng.acquire()
+            head = eng.step([(s, toks[:-1], [T - 2])]).cpu()
+            tail = eng.step([(s, [toks[-1]], [0])]).cpu()
+            eng.release(s)
+            assert worst(head[0], ref[-2]) <= TOL[dt] and worst(tail[0], ref[-1]) <= TOL[dt], (place, dt)
+
+
+# ---------------------------------------------------------------------------------------------- generation, the program
+@pytest.mark.parametrize("name", ["a", "d"])
+def test_greedy_generation_through_the_entry_point(models, name):
+    m = models[name]
+    prompts = [tiny.random_prompt(m.vocab, n, 7 * n) for n in (1, 9, 70, 30)]
+    engine = Engine.from_folder(m.folder, dtype="float32", max_tokens=64 * 8, max_seqs=3)     # two batches
+    results, metrics = engine.generate(prompts, 12, SamplingParams(), stop_ids=[])
+    for p, r in zip(prompts, results):
+        ids = list(p)
+        for tok in r.tokens:                                   # along the engine's own tokens: the chosen one is the largest
+            row = logits_of(m, ids)[-1]
+            assert float(row.max() - row[tok]) <= 2e-5 * float(row.abs().max()), f"prompt of {len(p)}"
+            ids.append(tok)
+        assert len(r.tokens) == 12 and r.finish_reason == "length"
+    assert metrics.generated_tokens == 12 * len(prompts)
+    engine.cache.check()
+    assert engine.cache.slots.held_count == 0
+    # bfloat16 and sampling run through the same loop
+    engine = Engine.from_folder(m.folder, dtype="bfloat16", max_tokens=64 * 8)
+    results, _ = engine.generate(prompts, 6, SamplingParams(temperature=0.8, top_k=20, seed=3), stop_ids=[])
+    assert all(len(r.tokens) == 6 and all(0 <= t < m.vocab for t in r.tokens) for r in results)
+
+
+def test_trace_program_on_a_model_of_this_design(models, tmp_path):
+    m = models["b"]
+    reqs = {f"q{i}": tiny.random_prompt(m.vocab, n, n) for i, n in enumerate([40, 3, 90])}
+    steps = traces.ragged_batches(reqs, 3, {"q0": 5, "q1": 2, "q2": 30})
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dtype in ("bfloat16", "float32"):
+        out = tmp_path / dtype
+        proc = subprocess.run(
+            [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", m.folder, "--dtype", dtype,
+             "--out", str(out), "--max-tokens", str(traces.tokens_needed(steps))],
+            input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        compare(traces.collect(steps, str(out), m.vocab), refs_of(m, reqs), TOL[dtype], "trace program")
+
+
+def test_command_line_generates_from_a_folder_and_from_a_configuration_with_random_weights(models, tmp_path):
+    m = models["c"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "bin", "spissa-b200")
+    prompt = tiny.random_prompt(m.vocab, 12, 4)
+    proc = subprocess.run([sys.executable, exe, "generate", m.folder, "--token-ids", ",".join(map(str, prompt)),
+                           "--max-new-tokens", "5", "--dtype", "fp32", "--ctx", "128"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = json.loads(proc.stdout.strip().splitlines()[0])
+    assert line["tokens"] == P.generate_greedy(m.cfg, m.w, prompt, 5) and line["finish_reason"] == "length"
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(M.CONFIGS["a"]))
+    proc = subprocess.run([sys.executable, exe, "generate", "--random", str(cfg_file), "--token-ids", "1,2,3",
+                           "--token-ids", "9,8,7,6,5", "--max-new-tokens", "4", "--temp", "0.7", "--seed", "2", "--ctx", "128"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(x) for x in proc.stdout.strip().splitlines()]
+    assert [len(x["tokens"]) for x in lines] == [4, 4]
