@@ -64,7 +64,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int* __restrict__ seq_start, const int* __restrict__ positions,
                         const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
                         int n_seqs, int nh, int nkv, float scale_log2, int* status, SpRange rg,
-                        const float* __restrict__ sink, int window, int rows_mode) {
+                        const float* __restrict__ sink, int window, int rows_mode,
+                        const float* __restrict__ dist_bias, int dist_cap) {
     static_assert(HD == 64 || HD == 128, "scores 2 x 64 columns and the output HD columns of 256 in tensor memory");
     using L = Smem<HD>;
     constexpr int KV_STAGES = kv_stages<HD>();
@@ -207,6 +208,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int qpos = pos0 + row;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
         float m = -INFINITY, l = 0.0f;                            // reference maximum (log2 units) and sum
+        // a score by distance (float32 [heads][dist_cap + 1], natural-log units; distances beyond dist_cap take the last
+        // entry): it is added to the scaled score as soon as a block's scores are in registers, which from then on are in
+        // log2 units, and the scale that the rest of the block's pass applies is one
+        const float* bias_row = dist_bias ? dist_bias + (size_t)h * (dist_cap + 1) : nullptr;
+        const float sl = bias_row ? 1.0f : scale_log2;
         bool ok = true;
         for (int j = 0; j < n_blocks; ++j) {
             ok = mbar_wait(smem_u32(&bar_s[j & 1]), (uint32_t)(j >> 1) & 1u, status, 115);
@@ -218,6 +224,19 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tc_ld_32x32(s_addr + 32, r + 32);
             tc_ld_wait();
             const int key0 = (j_lo + j) * KB;
+            if (bias_row) {
+                if (qpos - (key0 + KB - 1) >= dist_cap) {         // every key of the block is at least dist_cap away
+                    const float far = __ldg(bias_row + dist_cap) * LOG2E;
+#pragma unroll
+                    for (int i = 0; i < KB; ++i) r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), scale_log2, far));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < KB; ++i) {
+                        const int dist = min(max(qpos - key0 - i, 0), dist_cap);
+                        r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), scale_log2, __ldg(bias_row + dist) * LOG2E));
+                    }
+                }
+            }
             if (key0 + KB - 1 > pos0) {                           // some row of the tile cannot see some key of the block
 #pragma unroll
                 for (int i = 0; i < KB; ++i)
@@ -239,7 +258,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 mx4[2] = fmaxf(mx4[2], __uint_as_float(r[i + 2]));
                 mx4[3] = fmaxf(mx4[3], __uint_as_float(r[i + 3]));
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl;
             // move the reference only when it is far behind (or not set yet)
             const bool move = mx > m + RESCALE_STEP || (m == -INFINITY && mx > -INFINITY);
             if (__any_sync(0xffffffffu, move)) {
@@ -268,8 +287,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             uint32_t pk[KB / 2];
 #pragma unroll
             for (int i = 0; i < KB; i += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(r[i]), scale_log2, -m_safe));
-                const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2, -m_safe));
+                const float p0 = ex2(fmaf(__uint_as_float(r[i]), sl, -m_safe));
+                const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), sl, -m_safe));
                 sum4[(i >> 1) & 3] += p0 + p1;
                 __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
                 pk[i >> 1] = *(uint32_t*)&pr;
@@ -366,7 +385,8 @@ namespace {
 template <int HD>
 int launch_flash_tc(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out,
                     const int* seq_start, const int* positions, const int* seq_row, const int* page_table, int max_pages,
-                    int n_seqs, int nh, int nkv, float scale, int* status, const float* sink, int window, int rows_mode) {
+                    int n_seqs, int nh, int nkv, float scale, int* status, const float* sink, int window, int rows_mode,
+                    const float* dist_bias = nullptr, int dist_cap = 0) {
     static SpPerDevice configured;
     if (!configured.done()) {
         cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<HD>::TOTAL);
@@ -375,7 +395,7 @@ int launch_flash_tc(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const
     }
     SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<HD>, grid, dim3(192), (size_t)Smem<HD>::TOTAL, stream,
         mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-        scale * LOG2E, status, sp_range_host, sink, window, rows_mode));
+        scale * LOG2E, status, sp_range_host, sink, window, rows_mode, dist_bias, dist_cap));
     SP_CHECK_LAUNCH("flash_prefill_tc");
     return 0;
 }
@@ -385,12 +405,14 @@ int launch_flash_tc(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const
 // q, out: [T, nh*hd] bfloat16; pools: [n_pages, nkv, 64, hd] bfloat16; n_q_tiles = sum over sequences of
 // ceil(new tokens / 128). ``window`` w > 0: a query at position i sees the keys i - w < j <= i.
 // ``sink`` (float32 per query head, or null): a score that joins every row's denominator once, with no key and no value
-SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
+// ``dist_bias`` (float32 [nh][dist_cap + 1], or null): a score added by the distance between query and key
+SP_API int sp_flash_prefill_tc_bias(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
                                     int T, const int* seq_start, const int* positions, const int* seq_row,
                                     const int* page_table, int max_pages, int page_size, int n_seqs, int n_q_tiles, int nh,
                                     int nkv, int hd, int window, float scale, int* status, const float* sink,
-                                    cudaStream_t stream) {
+                                    const float* dist_bias, int dist_cap, cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
+    if (dist_bias && dist_cap < 0) SP_FAIL("flash_tc: a distance-bias table needs at least one entry per head");
     if (!sp_flash_tc_supported(hd, nh, nkv, page_size, window))
         SP_FAIL("flash_tc: built for head sizes 64 and 128 and pages of 64 (got head %d, page %d)", hd, page_size);
     if (((uintptr_t)q & 15) || ((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15) || ((uintptr_t)out & 15))
@@ -403,9 +425,18 @@ SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool,
     dim3 grid(nh, n_q_tiles);
     const int w = window > 0 ? window : 0;
     return hd == 64 ? launch_flash_tc<64>(grid, stream, mq, mk, mv, out, seq_start, positions, seq_row, page_table, max_pages,
-                                          n_seqs, nh, nkv, scale, status, sink, w, 0)
+                                          n_seqs, nh, nkv, scale, status, sink, w, 0, dist_bias, dist_cap)
                     : launch_flash_tc<128>(grid, stream, mq, mk, mv, out, seq_start, positions, seq_row, page_table, max_pages,
-                                           n_seqs, nh, nkv, scale, status, sink, w, 0);
+                                           n_seqs, nh, nkv, scale, status, sink, w, 0, dist_bias, dist_cap);
+}
+
+SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
+                                    int T, const int* seq_start, const int* positions, const int* seq_row,
+                                    const int* page_table, int max_pages, int page_size, int n_seqs, int n_q_tiles, int nh,
+                                    int nkv, int hd, int window, float scale, int* status, const float* sink,
+                                    cudaStream_t stream) {
+    return sp_flash_prefill_tc_bias(q, out, kpool, vpool, n_pages, T, seq_start, positions, seq_row, page_table, max_pages,
+                                    page_size, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, status, sink, nullptr, 0, stream);
 }
 
 // The same over keys and values that are not in a cache: ``k`` and ``v`` [T, nkv*hd] bfloat16 hold the step's own

@@ -176,9 +176,6 @@ def rope_kv_write(qkv, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd, rd, w
         c_void_p(_ptr(inv_freq)), T, nh, nkv, hd, rd, int(bool(write_kv)), c_void_p(_stream())))
 
 
-FLASH_DISTANCE_BIAS = True       # whether the tensor-core attention kernels take a table of scores by distance
-
-
 def _dist_bias_args(dist_bias, nh):
     """(pointer, last distance with an entry of its own) of a per-head table of scores by distance, float32
     [nh, entries]: a key at distance n takes entry min(n, entries − 1)."""
@@ -711,8 +708,10 @@ def flash_tc_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int,
             and bool(load("flash_tc").sp_flash_tc_supported(int(hd), int(nh), int(nkv), int(page_size), int(window or 0))))
 
 
-def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, sink=None):
-    """Causal attention of a step's tokens over the paged cache on the tcgen05 tensor cores.
+def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale, sink=None,
+                     dist_bias=None):
+    """Causal attention of a step's tokens over the paged cache on the tcgen05 tensor cores. ``dist_bias`` (float32
+    [nh, entries]): a score added by the distance between query and key, beyond the scale.
 
     ``n_q_tiles`` = sum over sequences of ceil(new tokens / ``flash_tc_query_tile()``). S, P and O live in tensor memory.
     """
@@ -720,12 +719,13 @@ def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles,
     _need_contig(q, out, k_pool, v_pool)
     pt = meta.page_table
     _declare_bounds("flash_tc", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
-    _check("flash_tc", lib.sp_flash_prefill_tc_sink(
+    bias_ptr, bias_cap = _dist_bias_args(dist_bias, nh)
+    _check("flash_tc", lib.sp_flash_prefill_tc_bias(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_longlong(k_pool.shape[0]), q.shape[0], c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)),
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles),
         nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_ptr(status_word(q.device))), _sink_ptr(sink, nh),
-        c_void_p(_stream())))
+        bias_ptr, bias_cap, c_void_p(_stream())))
 
 
 def flash_tc_rows_supported(dtype, nh: int, nkv: int, hd: int) -> bool:

@@ -143,10 +143,11 @@ class GQAAttention(Mixer):
                             self.sink, self.counters)
 
 
-def attend_paged(q, step, cache, nh, nkv, hd, window, scale, sink=None, counters=None):
+def attend_paged(q, step, cache, nh, nkv, hd, window, scale, sink=None, counters=None, dist_bias=None):
     """Softmax attention of the step's queries ``q`` [T, nh·hd] over the paged keys and values of ``cache`` (a
     ``KVLayerView``; key and value rows of one size): the tensor-core kernels where they take the sizes, else the
-    generic one. ``sink``: float32 [nh] or None. ``counters``: the arrival counters of the split-key decode kernel."""
+    generic one. ``sink``: float32 [nh] or None. ``dist_bias``: float32 [nh, distances] or None, a score added by the
+    distance between query and key. ``counters``: the arrival counters of the split-key decode kernel."""
     T = q.shape[0]
     ctx = torch.empty_like(q)
     if K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
@@ -159,16 +160,18 @@ def attend_paged(q, step, cache, nh, nkv, hd, window, scale, sink=None, counters
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
             K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, window,
                            scale, chunk_tiles, n_chunks, scratch,
-                           counters if counters is not None and T * nkv <= counters.numel() else None, sink=sink)
+                           counters if counters is not None and T * nkv <= counters.numel() else None, sink=sink,
+                           dist_bias=dist_bias)
         elif T >= 256 and K.flash_tc_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size, window):
             # long prompts: 128-token tiles on the tcgen05 tensor cores (S, P and O in tensor memory)
             tiles = K.query_tiles(step.host["new_counts"], K.flash_tc_query_tile())
             K.flash_prefill_tc(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs, tiles,
-                               nh, nkv, hd, window, scale, sink=sink)
+                               nh, nkv, hd, window, scale, sink=sink, dist_bias=dist_bias)
         else:
             tiles = K.query_tiles(step.host["new_counts"], K.flash_query_tile())
             K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
-                            tiles, nh, nkv, hd, window, scale, sink=sink)
+                            tiles, nh, nkv, hd, window, scale, sink=sink, dist_bias=dist_bias)
     else:
-        K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, window, scale, sink=sink)
+        K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, window, scale, sink=sink,
+                            dist_bias=dist_bias)
     return ctx

@@ -152,22 +152,9 @@ class GatedAttention(Mixer):
     def attend(self, q, step, cache):
         """The heads' outputs [T, heads·vdim] over the cached keys and values, the step's own included."""
         nh, g, d, vd = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
-        if d == vd and self.dist is None:
-            return attend_paged(q, step, cache, nh, g, d, self.window, self.scale, self.sink, self.counters)
+        if d == vd:
+            return attend_paged(q, step, cache, nh, g, d, self.window, self.scale, self.sink, self.counters, dist_bias=self.dist)
         T = q.shape[0]
-        if d == vd and K.FLASH_DISTANCE_BIAS and K.flash_supported(q, cache.k_pool, nh, g, d, cache.page_size):
-            ctx = torch.empty_like(q)
-            if step.all_single:
-                chunk_tiles, n_chunks = K.flash_decode_plan(T, g, length_bucket(step.max_len, cache.page_size), cache.page_size)
-                scratch = torch.empty(K.flash_decode_scratch_floats(T, nh, d, n_chunks), dtype=torch.float32, device=q.device)
-                K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, g, d, self.window, self.scale,
-                               chunk_tiles, n_chunks, scratch, self.counters if T * g <= self.counters.numel() else None,
-                               sink=self.sink, dist_bias=self.dist)
-            else:
-                tiles = K.query_tiles(step.host["new_counts"], K.flash_query_tile())
-                K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs, tiles, nh, g, d,
-                                self.window, self.scale, sink=self.sink, dist_bias=self.dist)
-            return ctx
         ctx = torch.empty(T, nh * vd, dtype=q.dtype, device=q.device)
         K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, g, d, self.window, self.scale, vd=vd,
                             sink=self.sink, dist_bias=self.dist)

@@ -265,11 +265,27 @@ class RotaryLatentAttention(Mixer):
         v_map[:, :, :r] = uv.view(H, vd, r)
         self.v_map = v_map.contiguous()
         self.o = Linear(tensors[n["o"]])
+        # for steps of many tokens (bfloat16) the per-head maps are multiplied out into the products before and behind
+        # them: rows [E_h-part of q | rotated part] per head instead of q, so that the kernel that rotates writes the
+        # query in the rows' space, and W_o,h [U_v,h | 0] behind the weighted sums of rows (the gate of a head is one
+        # number and passes through the map)
+        self.proj_fold = self.o_fold = None
+        if rt.act_dtype == torch.bfloat16 and all(w.dtype == torch.bfloat16 for w in (q, uk, uv, self.o.weight)):
+            wq = q.float().view(H, d + rd, -1)
+            folded = torch.cat([torch.bmm(uk.float().view(H, d, r).transpose(1, 2), wq[:, :d]), wq[:, d:]], dim=1)
+            stack[0] = folded.reshape(H * R, -1).to(torch.bfloat16)
+            self.proj_fold = Linear(torch.cat(stack, dim=0))
+            wo = self.o.weight.float().view(-1, H, vd).permute(1, 0, 2)
+            fold = torch.zeros(H, wo.shape[1], R, dtype=torch.float32, device=wo.device)
+            fold[:, :, :r] = torch.bmm(wo, uv.float().view(H, vd, r))
+            self.o_fold = Linear(fold.permute(1, 0, 2).reshape(-1, H * R).to(torch.bfloat16))
         self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
 
     def forward(self, x, step, cache, residual):
         H, d, rd, vd, r = self.num_heads, self.head_dim, self.rot_dim, self.v_head_dim, self.kv_rank
         T, dev, act, R = x.shape[0], x.device, self.rt.act_dtype, self.kv_rank + self.rot_dim
+        if self.proj_fold is not None and T > FOLDED_FROM_TOKENS:
+            return self._forward_folded(x, step, cache, residual)
         writes = cache.writes
         if writes and self.shares_latent:
             raise ValueError(f"{self.prefix}: a layer without a latent projection cannot be the writer of a cache")
@@ -285,12 +301,7 @@ class RotaryLatentAttention(Mixer):
             qx = torch.empty(T, H * R, dtype=act, device=dev)
             K.headwise_product(q, self.q_map, qx, H, d + rd, R, w_rows_are_k=False)              # E_h q_h
         with phase("latent_attention_ms"):
-            if act == torch.bfloat16 and cache.k_pool.dtype == torch.bfloat16 and K.latent_flash_supported(R, cache.page_size):
-                mix = torch.empty_like(qx)
-                max_len = length_bucket(step.max_len, cache.page_size) if step.all_single else None
-                K.latent_flash(qx, cache.k_pool, mix, cache, step, H, R, self.window, self.scale, None, max_len=max_len)
-            else:
-                mix = attend_paged(qx, step, cache, H, 1, R, self.window, self.scale, None, self.counters)
+            mix = self._attend_rows(qx, step, cache)
         with phase("value_expansion_ms"):
             ctx = torch.empty(T, H * vd, dtype=act, device=dev)
             K.headwise_product(mix, self.v_map, ctx, H, R, vd, w_rows_are_k=False)               # U_v,h (Σ p c)
@@ -298,3 +309,35 @@ class RotaryLatentAttention(Mixer):
             K.scale_rows_sigmoid(ctx.view(T * H, vd), gates.view(T * H))
         with phase("o_projection+attention_residual_ms"):
             self.o(ctx, out=residual, accumulate=True)
+
+    def _attend_rows(self, qx, step, cache):
+        """Σ_j p_h(i, j) [c_j | k_j^r] for queries in the rows' space: [T, heads·(rank + rot_dim)]."""
+        H, R, act = self.num_heads, self.kv_rank + self.rot_dim, self.rt.act_dtype
+        if act == torch.bfloat16 and cache.k_pool.dtype == torch.bfloat16 and K.latent_flash_supported(R, cache.page_size):
+            mix = torch.empty_like(qx)
+            max_len = length_bucket(step.max_len, cache.page_size) if step.all_single else None
+            K.latent_flash(qx, cache.k_pool, mix, cache, step, H, R, self.window, self.scale, None, max_len=max_len)
+            return mix
+        return attend_paged(qx, step, cache, H, 1, R, self.window, self.scale, None, self.counters)
+
+    def _forward_folded(self, x, step, cache, residual):
+        H, rd, r = self.num_heads, self.rot_dim, self.kv_rank
+        T, dev, act, R = x.shape[0], x.device, self.rt.act_dtype, self.kv_rank + self.rot_dim
+        writes = cache.writes
+        if writes and self.shares_latent:
+            raise ValueError(f"{self.prefix}: a layer without a latent projection cannot be the writer of a cache")
+        freq, amp = (self.position.rotary()[0], getattr(self.position, "amplitude", 1.0)) if rd else (None, 1.0)
+        with phase("latent_projection_ms"):
+            proj = self.proj_fold(x, out_dtype=torch.float32)
+        with phase("latent_norm+rotary+append_ms"):
+            qx = torch.empty(T, H * R, dtype=act, device=dev)
+            gates = torch.empty(T, H, dtype=torch.float32, device=dev)
+            # the unrotated part of a head's query is already in the rows' space: ``rank`` entries instead of ``dim``
+            K.latent_rot_store(proj, self.wc_norm if writes else None, qx, cache.k_pool if writes else None, cache, gates, freq,
+                               H, r, rd, r, amp, self.eps)
+        with phase("latent_attention_ms"):
+            mix = self._attend_rows(qx, step, cache)
+        with phase("head_gate_ms"):
+            K.scale_rows_sigmoid(mix.view(T * H, R), gates.view(T * H))
+        with phase("o_projection+attention_residual_ms"):
+            self.o_fold(mix, out=residual, accumulate=True)                                   # (W_o,h [U_v,h | 0]) g_h Σ p r

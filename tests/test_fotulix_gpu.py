@@ -36,6 +36,7 @@ TOL = {"float32": 2e-5, "bfloat16": 5e-2}
 # weights; here each adds about half the stream's size). The worst of hundreds of rows lies well above the mean; a fault
 # of a mechanism (the 32-bit runs bound those at 2e-5) moves single rows by the size of the logits.
 DEEP_TOL = {"float32": 2e-5, "bfloat16": 1e-1}
+DEEP_ALLOW = {"float32": 0.0, "bfloat16": 0.02}      # the share of rows that may lie beyond the tolerance (within twice it)
 MEAN_TOL = {2e-5: 2e-5, 5e-2: 1e-2, 1e-1: 2e-2}
 
 
@@ -47,13 +48,17 @@ def worst(got, ref):
     return float((got.double().cpu() - ref.double()).abs().max() / ref.abs().max())
 
 
-def compare(got, ref, tol, what):
+def compare(got, ref, tol, what, allow=0.0):
+    """Every row within ``tol`` of the largest logit (a share ``allow`` of the rows within twice that), and the rows'
+    mean within the mean tolerance that goes with ``tol``."""
     assert set(got) == set(ref), what
     scale = max(float(v.abs().max()) for v in ref.values())
-    errs = [(float((row.double() - ref[k].double()).abs().max()) / scale, k) for k, row in got.items()]
+    errs = sorted((float((row.double() - ref[k].double()).abs().max()) / scale, k) for k, row in got.items())
     assert all(e == e for e, _ in errs), what
-    e, k = max(errs, key=lambda x: x[0])
-    assert e <= tol, f"{what}: the worst row is {e:.3e} of the largest logit away, at {k}"
+    e, k = errs[-1]
+    over = [x for x in errs if x[0] > tol]
+    assert len(over) <= allow * len(errs) and e <= 2 * tol, \
+        f"{what}: {len(over)} of {len(errs)} rows beyond {tol:.1e}; the worst is {e:.3e} of the largest logit away, at {k}"
     mean = sum(x for x, _ in errs) / len(errs)
     assert mean <= MEAN_TOL.get(tol, tol), f"{what}: the rows are {mean:.3e} of the largest logit away on average"
 
@@ -446,9 +451,9 @@ def test_every_cut_agrees_with_plain(models, name, dtype, tmp_path):
         out = tmp_path / cut
         traces.run_in_process(m.folder, dtype, steps, str(out))          # a cache that holds just this trace: slots and pages come back
         results[cut] = traces.collect(steps, str(out), m.vocab)
-        compare(results[cut], ref, DEEP_TOL[dtype], f"{name}/{dtype}/{cut}")
+        compare(results[cut], ref, DEEP_TOL[dtype], f"{name}/{dtype}/{cut}", DEEP_ALLOW[dtype])
     for cut in ("tail", "ragged", "ragged_pairs"):
-        compare(results[cut], results["whole"], DEEP_TOL[dtype], f"{name}/{dtype}: {cut} against whole")
+        compare(results[cut], results["whole"], DEEP_TOL[dtype], f"{name}/{dtype}: {cut} against whole", DEEP_ALLOW[dtype])
 
 
 @pytest.mark.parametrize("name", ["a", "c"])
@@ -508,7 +513,8 @@ def test_long_decoding_lets_windows_pass_over_decoded_tokens_and_returns_pages(m
         s = engine.acquire()
         engine.step([(s, toks[:10], [])])
         rows = torch.cat([engine.step([(s, [t], [0])]).cpu() for t in toks[10:]])
-        compare({("long", i): r for i, r in enumerate(rows)}, {("long", i): r for i, r in enumerate(ref[10:])}, DEEP_TOL[dtype], dtype)
+        compare({("long", i): r for i, r in enumerate(rows)}, {("long", i): r for i, r in enumerate(ref[10:])}, DEEP_TOL[dtype], dtype,
+                DEEP_ALLOW[dtype])
         for g in engine.cache.kv_groups.values():
             flags = [p is not None for p in engine.cache.seqs[s].pages[g.name]]
             assert flags[-1]
