@@ -597,11 +597,12 @@ def fotulix_rooflines(size, fx, row, T, B, peaks, eb) -> dict:
                                                           fz.get("latent_norm+rotary+append_ms")))
     out["kugirax latent norms+append (hbm)"] = dict(ms=kz.get("latent_norm+append_ms"),
                                                     frac=frac(T * (2 * fx["q_rank"] + R) * (4.0 + eb), bw, kz.get("latent_norm+append_ms")))
-    # three passes per layer: the stream and the sublayer's sum read, both written (the sum as zeros), two of them also
-    # write the next reader's input
+    # three passes per layer: the stream and the sublayer's sum read, both written (the sum as zeros); each also writes
+    # the next reader's input (the last layer's last pass has no reader)
     post = (fz.get("attention_out_norm+mlp_norm_ms") or 0) + (fz.get("out_norm_ms") or 0) + (fz.get("side_out_norm_ms") or 0)
-    out["norms into the stream (hbm)"] = dict(ms=post, frac=frac(L * T * W * (3 * 4 * 4.0 + 2 * eb), bw, post))
-    out["norm (hbm)"] = dict(ms=fz.get("attention_norm_ms"), frac=frac(L * T * W * (4.0 + eb), bw, fz.get("attention_norm_ms")))
+    out["norms into the stream (hbm)"] = dict(ms=post, frac=frac(T * W * (L * (3 * 4 * 4.0 + 2 * eb) + (L - 1) * eb), bw, post))
+    # one launch: the first layer's (a layer's last pass over the stream writes the next layer's first norm)
+    out["norm (hbm)"] = dict(ms=fz.get("attention_norm_ms"), frac=frac(T * W * (4.0 + eb), bw, fz.get("attention_norm_ms")))
     out["kugirax norm (hbm)"] = dict(ms=kz.get("input_norm_ms"), frac=frac(L * T * W * (4.0 + eb), bw, kz.get("input_norm_ms")))
     out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
     out["head gates (hbm)"] = dict(ms=fz.get("head_gate_ms"), frac=frac(T * ((L - n_lat) * h * d + n_lat * lh * lvd) * 2 * eb, bw, fz.get("head_gate_ms")))
@@ -657,6 +658,22 @@ def kernel_case(name: str, reps: int) -> int:
             eng.step([(sl, [5 + i], [0]) for sl in slots])
         torch.cuda.synchronize()
         print(json.dumps({"kernel_case": name, "launches": K.launches}))
+        return 0
+    if name == "fotulix_step":
+        # the Fotulix decoder at the 2k size of --design: one prompt of 2,048 tokens, then three decode steps, kernel by
+        # kernel (no CUDA graph): the launch list of this run is what profiles/fotulix_step_and_kernels.md summarises
+        from spissa_b200 import Engine
+        from spissa_b200.config import config_from_dict
+        cfg = config_from_dict(fotulix_config(DESIGN_SIZES["2k"], FOTULIX_SIZES["2k"]))
+        eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=T + 128, max_seqs=1, use_graphs=False)
+        rng = random.Random(0)
+        sl = eng.acquire()
+        eng.step([(sl, [rng.randrange(DESIGN_VOCAB) for _ in range(T)], [T - 1])])
+        l0 = K.launches
+        for i in range(3):
+            eng.step([(sl, [5 + i], [0])])
+        torch.cuda.synchronize()
+        print(json.dumps({"kernel_case": name, "launches": K.launches, "launches_per_decode_step": (K.launches - l0) // 3}))
         return 0
     if name == "prefill":
         # prompts of 2,048 tokens one after another through the engine's own step (the launch list of this run is
@@ -1041,6 +1058,77 @@ def kernel_case(name: str, reps: int) -> int:
                 bytes_ = LH * d * r * 2.0
             else:
                 flops = rows * LH * 2.0 * d * r
+    elif name in ("distance_attention", "distance_attention_plain", "distance_attention_mma", "distance_decode_b8",
+                  "distance_decode_b8_plain", "gated_qkv_store", "latent_rot_store", "stream_norm_add", "row_gates"):
+        # the Fotulix kernels at the 2k size of --design (16 heads of 128 on 4 kv heads, a table of 32 scores by distance
+        # that reaches 4,096; width 2,048; 16 latent heads, rows of 192 + 64)
+        FH, FG, Fd, Wd, r, rd = 16, 4, 128, 2048, 192, 64
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        B = 8 if "_b8" in name else 1
+        n_new = 1 if B > 1 else T
+        ar = torch.arange(B, dtype=torch.int32, device=dev)
+        pos = (torch.arange(n_new, dtype=torch.int32, device=dev) + (T - n_new)).repeat(B)
+        step = SimpleNamespace(seq_start=i32([n_new * b for b in range(B + 1)]), seq_slot=ar, token_seq=ar.repeat_interleave(n_new),
+                               n_seqs=B, positions=pos, all_single=n_new == 1, max_new=n_new, max_len=T,
+                               seq_len=i32([T] * B), host=dict(new_counts=[n_new] * B))
+        pages = B * (T // 64)
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(B, T // 64)
+        meta = SimpleNamespace(page_table=table, page_size=64, seq_slot=ar, positions=pos, token_seq=step.token_seq)
+        rows = B * n_new
+        if name.startswith("distance_"):
+            from spissa_b200.parts.gated_attention import distance_table
+            n_buf = 40 if B > 1 else 1
+            pools = [(rnd(pages, FG, 64, Fd), rnd(pages, FG, 64, Fd)) for _ in range(n_buf)]
+            dist = None if name.endswith("_plain") else distance_table(torch.randn(32, FH, device=dev), 4096.0)
+            q = rnd(rows, FH * Fd)
+            out = torch.empty_like(q)
+            if B > 1:
+                ct, nc = K.flash_decode_plan(B, FG, T)
+                scratch = torch.empty(K.flash_decode_scratch_floats(B, FH, Fd, nc), device=dev)
+                run = lambda i: K.flash_decode(q, pools[i % n_buf][0], pools[i % n_buf][1], out, meta, step.seq_len, FH, FG, Fd, None,
+                                               Fd ** -0.5, ct, nc, scratch, dist_bias=dist)
+                bytes_ = B * T * FG * Fd * 2 * 2.0
+            elif name == "distance_attention_mma":
+                run = lambda i: K.flash_prefill(q, pools[0][0], pools[0][1], out, meta, step.seq_start, 1, T // 64, FH, FG, Fd, None,
+                                                Fd ** -0.5, dist_bias=dist)
+                flops = 4.0 * (T * (T + 1) / 2) * Fd * FH
+            else:
+                run = lambda i: K.flash_prefill_tc(q, pools[0][0], pools[0][1], out, meta, step.seq_start, 1, T // 128, FH, FG, Fd,
+                                                   None, Fd ** -0.5, dist_bias=dist)
+                flops = 4.0 * (T * (T + 1) / 2) * Fd * FH
+        elif name == "gated_qkv_store":
+            C = (FH + FG) * Fd + FG * Fd
+            projs = [torch.randn(T, C + FH, device=dev) for _ in range(4)]
+            bias = rnd(C)
+            q = torch.empty(T, FH * Fd, dtype=bf, device=dev)
+            gates = torch.empty(T, FH, device=dev)
+            kp, vp = rnd(pages, FG, 64, Fd), rnd(pages, FG, 64, Fd)
+            run = lambda i: K.gated_qkv_store(projs[i % 4], bias, q, kp, vp, meta, gates, None, FH, FG, Fd, Fd, 0, temp_coef=0.2,
+                                              temp_every=512)
+            bytes_ = T * ((C + FH) * 4.0 + C * 2.0 + FH * 4.0)
+        elif name == "latent_rot_store":
+            R = r + rd
+            C = FH * R + R
+            projs = [torch.randn(T, C + FH, device=dev) for _ in range(4)]
+            wc = rnd(r)
+            freq = (10000.0 ** (-torch.arange(0, rd, 2, device=dev).float() / rd)).contiguous()
+            q = torch.empty(T, FH * R, dtype=bf, device=dev)
+            gates = torch.empty(T, FH, device=dev)
+            pool = rnd(pages, 1, 64, R)
+            run = lambda i: K.latent_rot_store(projs[i % 4], wc, q, pool, meta, gates, freq, FH, r, rd, r, 1.2, 1e-6)
+            bytes_ = T * ((C + FH) * 4.0 + C * 2.0 + FH * 4.0)
+        elif name == "stream_norm_add":
+            xs = [torch.randn(T, Wd, device=dev) for _ in range(6)]
+            ys = [torch.randn(T, Wd, device=dev) for _ in range(6)]
+            w1, w2 = torch.randn(Wd, device=dev), torch.randn(Wd, device=dev)
+            out = torch.empty(T, Wd, dtype=bf, device=dev)
+            run = lambda i: K.stream_norm_add(xs[i % 6], ys[i % 6], w1, 0.5, 1e-6, w_next=w2, out=out)
+            bytes_ = T * Wd * (4 * 4.0 + 2.0)
+        else:
+            xs = [rnd(T * FH, Fd) for _ in range(12)]
+            z = torch.randn(T * FH, device=dev)
+            run = lambda i: K.scale_rows_sigmoid(xs[i % 12], z)
+            bytes_ = T * FH * (Fd * 2 * 2.0 + 4.0)
     elif name in ("sample_b8", "sample_b64", "argmax_b8"):
         # the sampler on rows of 128,256 logits (standard deviation 4 after the temperature): temperature 0.8, top-p 0.95
         B = 64 if name.endswith("b64") else 8

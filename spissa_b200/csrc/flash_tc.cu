@@ -35,7 +35,8 @@ constexpr int QT = 128;            // query rows per CTA
 constexpr int KB = 64;             // keys per block = one page
 constexpr int PAGE = 64;
 // key/value stages: with the query tile 81 KB (head 64) or 97 KB (head 128) per CTA, so that two CTAs share an SM
-template <int HD> __host__ __device__ constexpr int kv_stages() { return HD == 64 ? 4 : 2; }
+// (keys of 192 with values of 128: 48 KB of queries and four stages of 40 KB, one CTA per SM)
+template <int HD> __host__ __device__ constexpr int kv_stages() { return HD == 128 ? 2 : 4; }
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;   // the reference maximum follows the true one in steps of at least this (log2 units)
 
@@ -46,18 +47,19 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // Operands lie in shared memory as boxes of 64 columns (one 128-byte swizzle span): a query tile is HD / 64 boxes of
-// 128 rows, a K or V page HD / 64 boxes of 64 rows.
-template <int HD>
+// 128 rows, a K page HD / 64 boxes of 64 rows, a V page HDV / 64 (value rows may be shorter than key rows).
+template <int HD, int HDV = HD>
 struct Smem {
-    static constexpr int BOXES = HD / 64;
+    static constexpr int BOXES = HD / 64, V_BOXES = HDV / 64;
     static constexpr int Q_BOX = QT * 128, KV_BOX = KB * 128;    // bytes
     static constexpr int Q_BYTES = BOXES * Q_BOX;
     static constexpr int K_BYTES = BOXES * KV_BOX;
-    static constexpr int STAGE_BYTES = 2 * K_BYTES;              // K page then V page
+    static constexpr int V_BYTES = V_BOXES * KV_BOX;
+    static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;        // K page then V page
     static constexpr int TOTAL = Q_BYTES + kv_stages<HD>() * STAGE_BYTES + 1024;
 };
 
-template <int HD>
+template <int HD, int HDV>
 __global__ void __launch_bounds__(192)
 flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -66,10 +68,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         int n_seqs, int nh, int nkv, float scale_log2, int* status, SpRange rg,
                         const float* __restrict__ sink, int window, int rows_mode,
                         const float* __restrict__ dist_bias, int dist_cap) {
-    static_assert(HD == 64 || HD == 128, "scores 2 x 64 columns and the output HD columns of 256 in tensor memory");
-    using L = Smem<HD>;
+    static_assert((HD == 64 || HD == 128 || HD == 192) && (HDV == 64 || HDV == 128),
+                  "scores 2 x 64 columns and the output HDV columns of 256 in tensor memory");
+    using L = Smem<HD, HDV>;
     constexpr int KV_STAGES = kv_stages<HD>();
-    constexpr uint32_t TMEM_COLS = 256;                           // S0 64 | S1 64 | O HD
+    constexpr uint32_t TMEM_COLS = 256;                           // S0 64 | S1 64 | O HDV
     constexpr uint32_t COL_S = 0, COL_O = 128;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s[2], bar_p[2], bar_o, bar_done;
@@ -150,18 +153,18 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 // rows past the tensor's end arrive as zeros, rows of the next sequence are keys after every query here
                 const int r0 = rows_mode ? first + (j_lo + j) * KB
                                          : (sp_checked_page(pt[sp_checked_entry(j_lo + j, max_pages, rg)], rg) * nkv + g) * PAGE;
-                const int c0 = rows_mode ? g * HD : 0;
 #pragma unroll
-                for (int c = 0; c < L::BOXES; ++c) {
-                    tma_load_2d(k_dst + c * L::KV_BOX, &map_k, c0 + c * 64, r0, smem_u32(&bar_kv_full[s]));
-                    tma_load_2d(v_dst + c * L::KV_BOX, &map_v, c0 + c * 64, r0, smem_u32(&bar_kv_full[s]));
-                }
+                for (int c = 0; c < L::BOXES; ++c)
+                    tma_load_2d(k_dst + c * L::KV_BOX, &map_k, (rows_mode ? g * HD : 0) + c * 64, r0, smem_u32(&bar_kv_full[s]));
+#pragma unroll
+                for (int c = 0; c < L::V_BOXES; ++c)
+                    tma_load_2d(v_dst + c * L::KV_BOX, &map_v, (rows_mode ? g * HDV : 0) + c * 64, r0, smem_u32(&bar_kv_full[s]));
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && live) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KB);            // S[128,64] = Q·Kᵀ, both K-major
-            constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(QT, HD);        // O[128,HD] += P·V, V MN-major
+            constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(QT, HDV);       // O[128,HDV] += P·V, V MN-major
             bool ok = mbar_wait(smem_u32(&bar_q), 0, status, 112);
             auto issue_s = [&](int j) -> bool {
                 const int s = j % KV_STAGES;
@@ -270,7 +273,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                    for (int c0 = 0; c0 < HDV; c0 += 32) {
                         uint32_t o[32];
                         tc_ld_32x32(lane_base + COL_O + c0, o);
                         tc_ld_wait();
@@ -309,9 +312,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (ok && !(status && *(volatile int*)status != 0)) {
             // a sink: one more term in the denominator, with no key and no value (m and the sink's score in log2 units)
             const float inv = 1.0f / (sink ? l + exp2f(sink[h] * LOG2E - m) : l);
-            __nv_bfloat16* dst = out + (size_t)(t0 + row) * nh * HD + (size_t)h * HD;
+            __nv_bfloat16* dst = out + (size_t)(t0 + row) * nh * HDV + (size_t)h * HDV;
 #pragma unroll 1
-            for (int c0 = 0; c0 < HD; c0 += 32) {
+            for (int c0 = 0; c0 < HDV; c0 += 32) {
                 uint32_t r[32];
                 tc_ld_32x32(lane_base + COL_O + c0, r);
                 tc_ld_wait();
@@ -382,18 +385,18 @@ SP_API int sp_flash_tc_supported(int hd, int nh, int nkv, int page_size, int win
 
 namespace {
 
-template <int HD>
+template <int HD, int HDV = HD>
 int launch_flash_tc(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out,
                     const int* seq_start, const int* positions, const int* seq_row, const int* page_table, int max_pages,
                     int n_seqs, int nh, int nkv, float scale, int* status, const float* sink, int window, int rows_mode,
                     const float* dist_bias = nullptr, int dist_cap = 0) {
     static SpPerDevice configured;
     if (!configured.done()) {
-        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<HD>::TOTAL);
-        if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<HD>::TOTAL, cudaGetErrorString(e));
+        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD, HDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<HD, HDV>::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<HD, HDV>::TOTAL, cudaGetErrorString(e));
         configured.mark();
     }
-    SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<HD>, grid, dim3(192), (size_t)Smem<HD>::TOTAL, stream,
+    SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<HD, HDV>, grid, dim3(192), (size_t)Smem<HD, HDV>::TOTAL, stream,
         mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
         scale * LOG2E, status, sp_range_host, sink, window, rows_mode, dist_bias, dist_cap));
     SP_CHECK_LAUNCH("flash_prefill_tc");
@@ -442,25 +445,39 @@ SP_API int sp_flash_prefill_tc_sink(const void* q, void* out, const void* kpool,
 // The same over keys and values that are not in a cache: ``k`` and ``v`` [T, nkv*hd] bfloat16 hold the step's own
 // tokens, and every sequence of the step starts at its position 0 (the caller's promise: ``positions`` of a
 // sequence's first token is 0), so that key j of sequence b is row seq_start[b] + j.
-SP_API int sp_flash_prefill_tc_rows(const void* q, void* out, const void* k, const void* v, int T, const int* seq_start,
-                                    const int* positions, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
-                                    float scale, int* status, const float* sink, cudaStream_t stream) {
+SP_API int sp_flash_tc_rows_supported(int hd, int vd, int nh, int nkv) {
+    return nkv > 0 && nh % nkv == 0 && ((hd == 64 && vd == 64) || (hd == 128 && vd == 128) || (hd == 192 && vd == 128));
+}
+
+// ``vd``: the size of a value row (and of an output row per head); keys of 192 go with values of 128
+SP_API int sp_flash_prefill_tc_rows_kv(const void* q, void* out, const void* k, const void* v, int T, const int* seq_start,
+                                       const int* positions, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int vd,
+                                       int window, float scale, int* status, const float* sink, cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
-    if (!sp_flash_tc_supported(hd, nh, nkv, PAGE, window))
-        SP_FAIL("flash_tc: built for head sizes 64 and 128 (got head %d, %d heads over %d)", hd, nh, nkv);
+    if (!sp_flash_tc_rows_supported(hd, vd, nh, nkv))
+        SP_FAIL("flash_tc: built for keys and values of 64, of 128, and keys of 192 with values of 128 (got %d and %d, %d heads over %d)",
+                hd, vd, nh, nkv);
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
         SP_FAIL("flash_tc: operands must start on a 16-byte boundary");
     CUtensorMap mq, mk, mv;
     if (make_map(&mq, q, T, nh * hd, (long long)nh * hd, QT)) return 1;
     if (make_map(&mk, k, T, nkv * hd, (long long)nkv * hd, PAGE)) return 1;
-    if (make_map(&mv, v, T, nkv * hd, (long long)nkv * hd, PAGE)) return 1;
+    if (make_map(&mv, v, T, nkv * vd, (long long)nkv * vd, PAGE)) return 1;
     if (n_q_tiles > 65535) SP_FAIL("flash_tc: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
     const int w = window > 0 ? window : 0;
-    return hd == 64 ? launch_flash_tc<64>(grid, stream, mq, mk, mv, out, seq_start, positions, nullptr, nullptr, 0,
-                                          n_seqs, nh, nkv, scale, status, sink, w, 1)
-                    : launch_flash_tc<128>(grid, stream, mq, mk, mv, out, seq_start, positions, nullptr, nullptr, 0,
-                                           n_seqs, nh, nkv, scale, status, sink, w, 1);
+#define SP_ROWS_ARGS grid, stream, mq, mk, mv, out, seq_start, positions, nullptr, nullptr, 0, n_seqs, nh, nkv, scale, status, sink, w, 1
+    if (hd == 64) return launch_flash_tc<64>(SP_ROWS_ARGS);
+    if (hd == 128) return launch_flash_tc<128>(SP_ROWS_ARGS);
+    return launch_flash_tc<192, 128>(SP_ROWS_ARGS);
+#undef SP_ROWS_ARGS
+}
+
+SP_API int sp_flash_prefill_tc_rows(const void* q, void* out, const void* k, const void* v, int T, const int* seq_start,
+                                    const int* positions, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
+                                    float scale, int* status, const float* sink, cudaStream_t stream) {
+    return sp_flash_prefill_tc_rows_kv(q, out, k, v, T, seq_start, positions, n_seqs, n_q_tiles, nh, nkv, hd, hd, window, scale,
+                                       status, sink, stream);
 }
 
 SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,

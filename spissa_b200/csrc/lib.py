@@ -728,22 +728,32 @@ def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles,
         bias_ptr, bias_cap, c_void_p(_stream())))
 
 
-def flash_tc_rows_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
-    """Whether ``flash_prefill_tc_rows`` takes queries, keys and values of this type and shape."""
-    return dtype == torch.bfloat16 and bool(load("flash_tc").sp_flash_tc_supported(int(hd), int(nh), int(nkv), 64, 0))
+FLASH_TC_ROW_SIZES = ((64, 64), (128, 128), (192, 128))      # (key row, value row) per head that the kernel is built for
 
 
-def flash_prefill_tc_rows(q, k, v, out, step, n_q_tiles, nh, nkv, hd, window, scale, sink=None):
-    """The tcgen05 prefill attention over keys and values that lie in no cache: ``k`` and ``v`` [T, nkv·hd] bfloat16
-    are the step's own tokens, and EVERY sequence of the step starts at its position 0 (the caller has checked)."""
+def flash_tc_rows_supported(dtype, nh: int, nkv: int, hd: int, vd: int | None = None) -> bool:
+    """Whether ``flash_prefill_tc_rows`` takes queries, keys and values of this type and shape (``vd``: the size of a
+    value row when it differs from a key row's)."""
+    if dtype != torch.bfloat16 or (int(hd), int(vd or hd)) not in FLASH_TC_ROW_SIZES:
+        return False                              # (asked before the library: a model of other sizes never builds it)
+    return bool(load("flash_tc").sp_flash_tc_rows_supported(int(hd), int(vd or hd), int(nh), int(nkv)))
+
+
+def flash_prefill_tc_rows(q, k, v, out, step, n_q_tiles, nh, nkv, hd, window, scale, sink=None, vd=None):
+    """The tcgen05 prefill attention over keys and values that lie in no cache: ``k`` [T, nkv·hd] and ``v`` [T, nkv·vd]
+    bfloat16 are the step's own tokens, and EVERY sequence of the step starts at its position 0 (the caller has
+    checked). ``out`` is [T, nh·vd]."""
     lib = load("flash_tc")
     _need_contig(q, out, k, v)
     T = q.shape[0]
-    if k.shape != (T, nkv * hd) or v.shape != (T, nkv * hd) or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
-        raise KernelError("flash_tc: keys and values as rows are bfloat16 [tokens, kv heads x head size]")
-    _check("flash_tc", lib.sp_flash_prefill_tc_rows(
+    vd = int(vd or hd)
+    if k.shape != (T, nkv * hd) or v.shape != (T, nkv * vd) or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise KernelError("flash_tc: keys and values as rows are bfloat16 [tokens, kv heads x row size]")
+    if out.shape != (T, nh * vd) or q.shape[1] != nh * hd:
+        raise KernelError("flash_tc: queries are [tokens, heads x key size], the output [tokens, heads x value size]")
+    _check("flash_tc", lib.sp_flash_prefill_tc_rows_kv(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k)), c_void_p(_ptr(v)), T, c_void_p(_ptr(step.seq_start)),
-        c_void_p(_ptr(step.positions)), int(step.n_seqs), int(n_q_tiles), nh, nkv, hd, int(window or 0), c_float(scale),
+        c_void_p(_ptr(step.positions)), int(step.n_seqs), int(n_q_tiles), nh, nkv, hd, vd, int(window or 0), c_float(scale),
         c_void_p(_ptr(status_word(q.device))), _sink_ptr(sink, nh), c_void_p(_stream())))
 
 

@@ -33,6 +33,12 @@ class Model:
                 raise ValueError(f"no block arrangement registered as {layer.block!r}; "
                                  f"known: {part_registry.known_parts('block')}") from None
             self.layers.append(cls(mixer=layer.mixer, ffn=layer.ffn, norms=layer.norms, **layer.params))
+        # a block that ends with a pass over the stream can write the first norm of the block that always follows it
+        runs = [e.layer for e in spec.schedule]
+        for a, b in zip(spec.schedule, spec.schedule[1:]):
+            if (runs.count(a.layer) == 1 and runs.count(b.layer) == 1 and not b.adds_embedding and spec.streams == 1
+                    and hasattr(self.layers[a.layer], "feeds")):
+                self.layers[a.layer].feeds(self.layers[b.layer])
         self.final_norm = part_registry.build_part("norm", spec.final_norm)
         self.head = part_registry.build_part("head", spec.head)
         self.rt = None

@@ -205,6 +205,9 @@ class HyperConnectionBlock(Block):
             K.streams_norm(h, S, W, y=y, mix=c["mix2"], out_coef=c["out2"])
 
 
+NORMED_STREAM = "normed_stream"      # a step's scratch entry: the stream under the next block's first norm
+
+
 @register_part("block", "sandwich")
 class SandwichBlock(Block):
     """Every sublayer between two norms, its normed output scaled into the stream (not in the reference):
@@ -232,6 +235,7 @@ class SandwichBlock(Block):
         for n in (self.mixer_norm, self.mixer_out, self.ffn_norm, self.ffn_out, self.side_out):
             if n is not None and not hasattr(n, "multiplier"):
                 raise ValueError(f"{prefix}: the norms of this arrangement are RMS norms")
+        self.next_norm, self.takes_normed = None, False      # see ``feeds``
 
     def children(self):
         return [p for p in (self.mixer_norm, self.mixer, self.mixer_out, self.ffn_norm, self.ffn, self.ffn_out, self.side,
@@ -240,13 +244,26 @@ class SandwichBlock(Block):
     def cache_request(self):
         return self.mixer.cache_request()
 
+    def feeds(self, nxt) -> bool:
+        """Told once, when the model is put together, that ``nxt`` always runs right behind this block on the same
+        stream: this block's last pass over the stream then writes ``nxt``'s first norm as well. True if taken."""
+        if (isinstance(nxt, SandwichBlock) and nxt.hidden_size == self.hidden_size
+                and nxt.mixer_norm.eps == (self.side_out or self.ffn_out or self.mixer_out).eps):
+            self.next_norm, nxt.takes_normed = nxt.mixer_norm, True
+            return True
+        return False
+
     def forward(self, h, step, cache):
         W, r = self.hidden_size, self.residual_mult
         y = step.scratch.get("sublayer_sum")
         if y is None or y.shape[1] != W:
             y = step.scratch["sublayer_sum"] = torch.zeros(h.shape[0], W, dtype=torch.float32, device=h.device)
-        with phase("attention_norm_ms"):
-            x = self.mixer_norm.forward(h)
+        x = step.scratch.pop(NORMED_STREAM, None) if self.takes_normed else None    # the block before has normed the stream
+        if x is None:
+            with phase("attention_norm_ms"):
+                x = self.mixer_norm.forward(h)
+        nxt = self.next_norm
+        ahead = nxt.multiplier() if nxt is not None else None
         self.mixer.forward(x, step, cache, y)
         last = self.mixer_out
         if self.ffn is not None:
@@ -257,10 +274,16 @@ class SandwichBlock(Block):
             last = self.ffn_out
         with phase("out_norm_ms"):
             if self.side is None:
-                K.stream_norm_add(h, y, last.multiplier(), r, last.eps)
+                xn = torch.empty(h.shape[0], W, dtype=self.rt.act_dtype, device=h.device) if nxt is not None else None
+                K.stream_norm_add(h, y, last.multiplier(), r, last.eps, w_next=ahead, out=xn)
+                if nxt is not None:
+                    step.scratch[NORMED_STREAM] = xn
                 return
             x = torch.empty(h.shape[0], W, dtype=self.rt.act_dtype, device=h.device)
             K.stream_norm_add(h, y, last.multiplier(), r, last.eps, out=x, raw=True)     # the side sublayer reads the stream itself
         self.side.forward(x, step, y)
         with phase("side_out_norm_ms"):
-            K.stream_norm_add(h, y, self.side_out.multiplier(), r, self.side_out.eps)
+            xn = torch.empty(h.shape[0], W, dtype=self.rt.act_dtype, device=h.device) if nxt is not None else None
+            K.stream_norm_add(h, y, self.side_out.multiplier(), r, self.side_out.eps, w_next=ahead, out=xn)
+            if nxt is not None:
+                step.scratch[NORMED_STREAM] = xn

@@ -279,11 +279,22 @@ class RotaryLatentAttention(Mixer):
             fold = torch.zeros(H, wo.shape[1], R, dtype=torch.float32, device=wo.device)
             fold[:, :, :r] = torch.bmm(wo, uv.float().view(H, vd, r))
             self.o_fold = Linear(fold.permute(1, 0, 2).reshape(-1, H * R).to(torch.bfloat16))
+        # whole prompts expand their own rows into keys [U_k,h c | k^r] and values U_v,h c per head and run on the
+        # tcgen05 attention kernel where it takes the sizes: the maps as plain products over the rows (E_hᵀ and [U_v,h | 0])
+        self.k_rows = self.v_rows = None
+        if (rt.act_dtype == torch.bfloat16 and uk.dtype == torch.bfloat16 and uv.dtype == torch.bfloat16
+                and K.flash_tc_rows_supported(torch.bfloat16, H, H, d + rd, vd)):
+            self.k_rows = Linear(self.q_map.transpose(1, 2).reshape(H * (d + rd), R).contiguous())
+            self.v_rows = Linear(self.v_map.reshape(H * vd, R))
         self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
 
     def forward(self, x, step, cache, residual):
         H, d, rd, vd, r = self.num_heads, self.head_dim, self.rot_dim, self.v_head_dim, self.kv_rank
         T, dev, act, R = x.shape[0], x.device, self.rt.act_dtype, self.kv_rank + self.rot_dim
+        rows_key = ("latent_rows", cache.k_pool.data_ptr())
+        if (self.k_rows is not None and T >= EXPANDED_FROM_TOKENS and step.host.get("seq_len") is not None
+                and step.host["seq_len"] == step.host["new_counts"] and (cache.writes or rows_key in step.scratch)):
+            return self._forward_expanded(x, step, cache, residual, rows_key)
         if self.proj_fold is not None and T > FOLDED_FROM_TOKENS:
             return self._forward_folded(x, step, cache, residual)
         writes = cache.writes
@@ -319,6 +330,37 @@ class RotaryLatentAttention(Mixer):
             K.latent_flash(qx, cache.k_pool, mix, cache, step, H, R, self.window, self.scale, None, max_len=max_len)
             return mix
         return attend_paged(qx, step, cache, H, 1, R, self.window, self.scale, None, self.counters)
+
+    def _forward_expanded(self, x, step, cache, residual, rows_key):
+        """A step in which every sequence starts at its first token: the step's own rows, expanded, are all the keys and
+        values there are. The writer leaves its rows in the step's scratch for the layers that read its cache."""
+        H, d, rd, vd, r = self.num_heads, self.head_dim, self.rot_dim, self.v_head_dim, self.kv_rank
+        T, dev, act, R = x.shape[0], x.device, self.rt.act_dtype, self.kv_rank + self.rot_dim
+        writes = cache.writes
+        if writes and self.shares_latent:
+            raise ValueError(f"{self.prefix}: a layer without a latent projection cannot be the writer of a cache")
+        freq, amp = (self.position.rotary()[0], getattr(self.position, "amplitude", 1.0)) if rd else (None, 1.0)
+        with phase("latent_projection_ms"):
+            proj = self.proj(x, out_dtype=torch.float32)
+        with phase("latent_norm+rotary+append_ms"):
+            q = torch.empty(T, H * (d + rd), dtype=act, device=dev)
+            gates = torch.empty(T, H, dtype=torch.float32, device=dev)
+            rows = torch.empty(T, R, dtype=act, device=dev) if writes else None
+            K.latent_rot_store(proj, self.wc_norm if writes else None, q, cache.k_pool if writes else None, cache, gates, freq,
+                               H, d, rd, r, amp, self.eps, rows_out=rows)
+            if writes:
+                step.scratch[rows_key] = rows
+        rows = step.scratch[rows_key]
+        with phase("key_value_expansion_ms"):
+            k, v = self.k_rows(rows), self.v_rows(rows)
+        with phase("latent_attention_ms"):
+            ctx = torch.empty(T, H * vd, dtype=act, device=dev)
+            tiles = K.query_tiles(step.host["new_counts"], K.flash_tc_query_tile())
+            K.flash_prefill_tc_rows(q, k, v, ctx, step, tiles, H, H, d + rd, self.window, self.scale, None, vd=vd)
+        with phase("head_gate_ms"):
+            K.scale_rows_sigmoid(ctx.view(T * H, vd), gates.view(T * H))
+        with phase("o_projection+attention_residual_ms"):
+            self.o(ctx, out=residual, accumulate=True)
 
     def _forward_folded(self, x, step, cache, residual):
         H, rd, r = self.num_heads, self.rot_dim, self.kv_rank

@@ -708,3 +708,81 @@ def test_command_line_generates_from_a_folder_and_from_a_configuration_with_rand
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [json.loads(x) for x in proc.stdout.strip().splitlines()]
     assert [len(x["tokens"]) for x in lines] == [4, 4]
+
+
+# ---------------------------------------------------------------------------------------------- whole prompts, expanded
+@pytest.mark.parametrize("nh,nkv,hd,vd,window", [(4, 2, 192, 128, None), (4, 4, 192, 128, 70), (2, 1, 192, 128, 128), (3, 3, 192, 128, 1),
+                                                 (2, 2, 192, 128, 200), (4, 1, 192, 128, 65), (2, 2, 128, 128, 33), (3, 1, 64, 64, 64)])
+def test_keys_of_one_size_and_values_of_another_as_rows_of_the_steps_own_tokens(nh, nkv, hd, vd, window):
+    """The tcgen05 prompt kernel over keys and values that lie in no cache, with key rows longer than value rows:
+    ragged sequences that all start at 0, windows below, at and above a block and a tile. One key of the first
+    sequence is made to stand out, so that a window's edge that is one token off shows."""
+    from spissa_b200.csrc import lib as K
+    lengths = [300, 64, 129, 5, 410]
+    g = torch.Generator().manual_seed(nh * hd + (window or 0))
+    q = [torch.randn(n, nh, hd, generator=g).bfloat16() for n in lengths]
+    k = [torch.randn(n, nkv, hd, generator=g).bfloat16() for n in lengths]
+    v = [torch.randn(n, nkv, vd, generator=g).bfloat16() for n in lengths]
+    scale = 1.0 / math.sqrt(hd)
+    q[0][:, :, hd - 1] = 6.0
+    k[0][150] = 0.0
+    k[0][150, :, hd - 1] = 6.0 * math.sqrt(hd) / 8.0         # a score of 4.5 where the others are about 1, in the last key dim
+    refs = [_biased_mix(qb.double(), kb.double(), vb.double(), scale, None, 0.0, None, window) for qb, kb, vb in zip(q, k, v)]
+    starts = [0]
+    for n in lengths:
+        starts.append(starts[-1] + n)
+    step = SimpleNamespace(seq_start=i32(starts), positions=i32([p for n in lengths for p in range(n)]), n_seqs=len(lengths))
+    flat = lambda xs: torch.cat(xs).reshape(sum(lengths), -1).to(DEV).contiguous()
+    qd, kd, vdev = flat(q), flat(k), flat(v)
+    assert K.flash_tc_rows_supported(torch.bfloat16, nh, nkv, hd, vd)
+    out = torch.full((sum(lengths), nh * vd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.flash_prefill_tc_rows(qd, kd, vdev, out, step, K.query_tiles(lengths, K.flash_tc_query_tile()), nh, nkv, hd, window, scale, None, vd=vd)
+    K.check_status(torch.device(DEV))
+    for b, n in enumerate(lengths):
+        assert worst(out[starts[b]:starts[b] + n], refs[b]) <= 1.2e-2, b
+    if window and 150 + window < 300:
+        rows = slice(150 + window - 1, 150 + window + 1)
+        wide = _biased_mix(q[0].double(), k[0].double(), v[0].double(), scale, None, 0.0, None, window + 1)
+        assert worst(wide[rows], refs[0][rows]) > 0.05
+
+
+@pytest.mark.parametrize("d,rd,vd", [(128, 64, 128), (64, 64, 128), (32, 32, 64)])
+def test_whole_prompts_expand_their_own_rows(tmp_path, monkeypatch, d, rd, vd):
+    """Latent heads whose key (dim + rot_dim) and value sizes the tcgen05 prompt kernel takes: a step in which every
+    prompt starts at its first token expands that step's rows into keys and values (the writer's rows serve its reader
+    too, each with its own window); a portion behind cached tokens takes the multiplied-out maps over the cached rows,
+    decode steps the small products. All agree with plain."""
+    from spissa_b200.csrc import lib as K
+    cfg = M.model(128, 150, [M.layer("latent_attention", M.through_rows(2, d, rd, vd, 96, 100, scaling=M.RAMP), 64),
+                             M.layer("attention", M.biased(2, 1, 32, q_temp=(0.3, 64), far=100, rows=12)),
+                             M.layer("latent_attention", M.through_rows(3, d, rd, vd, 96, 270, scaling=M.RAMP, kv_from=0), 64)],
+                  mult=0.5, emb_scale=4.0, bigram=(53, 3, 5), side=8)
+    pcfg, w = M.make(cfg, tmp_path, seed=43, std=0.07)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    reqs = {"p": tiny.random_prompt(150, 336, 5), "r": tiny.random_prompt(150, 296, 6)}
+    ref = {(rid, i): row for rid, toks in reqs.items() for i, row in enumerate(logits_of(m, toks))}
+    calls = []
+    real = K.flash_prefill_tc_rows
+    monkeypatch.setattr(K, "flash_prefill_tc_rows", lambda *a, **kw: (calls.append(a[0].shape[0]), real(*a, **kw))[1])
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(str(tmp_path), dtype=dtype, max_tokens=64 * 14, max_seqs=2)
+        calls.clear()
+        sp, sr = eng.acquire(), eng.acquire()
+        rows = eng.step([(sp, reqs["p"][:330], list(range(330))), (sr, reqs["r"][:290], list(range(290)))]).cpu()
+        got = {("p", i): rows[i] for i in range(330)}
+        got.update({("r", i): rows[330 + i] for i in range(290)})
+        for i in range(6):
+            rows = eng.step([(sp, [reqs["p"][330 + i]], [0]), (sr, [reqs["r"][290 + i]], [0])]).cpu()
+            got[("p", 330 + i)], got[("r", 290 + i)] = rows[0], rows[1]
+        eng.release(sp), eng.release(sr)
+        assert calls == ([620] * 2 if dtype == "bfloat16" else []), calls
+        # (one row in several hundred may sit where two scores compete and bfloat16 rounding decides: within twice the tolerance)
+        compare(got, ref, TOL[dtype], f"{dtype}: two whole prompts", 0.01 if dtype == "bfloat16" else 0.0)
+        calls.clear()
+        s = eng.acquire()
+        eng.step([(s, reqs["p"][:40], [])])
+        rows = eng.step([(s, reqs["p"][40:330], list(range(290)))]).cpu()
+        eng.release(s)
+        assert calls == []
+        compare({("p", 40 + i): rows[i] for i in range(290)}, {k: v for k, v in ref.items() if k[0] == "p" and 40 <= k[1] < 330},
+                TOL[dtype], f"{dtype}: a portion behind cached tokens", 0.01 if dtype == "bfloat16" else 0.0)
