@@ -1059,7 +1059,8 @@ def kernel_case(name: str, reps: int) -> int:
             else:
                 flops = rows * LH * 2.0 * d * r
     elif name in ("distance_attention", "distance_attention_plain", "distance_attention_mma", "distance_decode_b8",
-                  "distance_decode_b8_plain", "gated_qkv_store", "latent_rot_store", "stream_norm_add", "row_gates"):
+                  "distance_decode_b8_plain", "gated_qkv_store", "latent_rot_store", "stream_norm_add", "row_gates",
+                  "rows_expanded"):
         # the Fotulix kernels at the 2k size of --design (16 heads of 128 on 4 kv heads, a table of 32 scores by distance
         # that reaches 4,096; width 2,048; 16 latent heads, rows of 192 + 64)
         FH, FG, Fd, Wd, r, rd = 16, 4, 128, 2048, 192, 64
@@ -1096,6 +1097,16 @@ def kernel_case(name: str, reps: int) -> int:
                 run = lambda i: K.flash_prefill_tc(q, pools[0][0], pools[0][1], out, meta, step.seq_start, 1, T // 128, FH, FG, Fd,
                                                    None, Fd ** -0.5, dist_bias=dist)
                 flops = 4.0 * (T * (T + 1) / 2) * Fd * FH
+        elif name == "rows_expanded":
+            # what a whole prompt's latent attention runs: the tcgen05 kernel over the prompt's own expanded keys (128 + 64
+            # per head) and values (128) as rows, a window of 1,024
+            kd, win = Fd + rd, 1024
+            ks, vs = [rnd(T, FH * kd) for _ in range(4)], [rnd(T, FH * Fd) for _ in range(4)]
+            q = rnd(T, FH * kd)
+            out = torch.empty(T, FH * Fd, dtype=bf, device=dev)
+            tiles = K.query_tiles([T], K.flash_tc_query_tile())
+            run = lambda i: K.flash_prefill_tc_rows(q, ks[i % 4], vs[i % 4], out, step, tiles, FH, FH, kd, win, kd ** -0.5, None, vd=Fd)
+            flops = 2.0 * (T * win - win * (win - 1) / 2) * (kd + Fd) * FH
         elif name == "gated_qkv_store":
             C = (FH + FG) * Fd + FG * Fd
             projs = [torch.randn(T, C + FH, device=dev) for _ in range(4)]
