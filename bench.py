@@ -298,7 +298,7 @@ def fotulix_config(size: dict, fx: dict, window: int = DESIGN_WINDOW) -> dict:
             layers.append(dict(type="attention_2" if i in FOTULIX_SINK else "attention", mixer=turned if i in FOTULIX_SINK else biased,
                                mlp=dict(kind="dense", ff=ff)))
     return dict(architecture="Fotulix", vocab=DESIGN_VOCAB, width=W, norm=dict(eps=1e-6), residual_mult=0.5,
-                embedding=dict(scale=W ** 0.5, bigram=dict(buckets=65521, mul_prev=127, mul_cur=7)),
+                embedding=dict(scale=W ** 0.5, bigram=dict(buckets=65521, mul_prev=31, mul_cur=17)),
                 token_side=dict(dim=FOTULIX_SIDE), layers=layers)
 
 

@@ -64,7 +64,7 @@ BANDS = (4.0, 1.0, 4.0, 16)        # factor, low, high, original length
 # the pair table (also one of a single bucket) and the token side input; multipliers of 1, 0.5 and 0.25
 CONFIGS = {
     "a": model(64, 200, [layer("latent_attention", through_rows(3, 8, 4, 12, 20, 9, base=100.0, scaling=RAMP), 56),
-                         layer("attention", biased(4, 2, 16, q_temp=(0.3, 16), far=40, rows=12), 48),
+                         layer("attention", biased(4, 2, 16, q_temp=(0.35, 16), far=40, rows=12), 48),
                          layer("latent_attention", through_rows(2, 16, 4, 4, 20, 70, base=100.0, scaling=RAMP, kv_from=0)),
                          layer("attention_2", turned(3, 3, 8, rot=4, base=50.0, scaling=BANDS)),
                          layer("attention", biased(2, 1, 10, vdim=6, far=20, rows=8), 40)],
@@ -173,7 +173,7 @@ def keys_needle_model(kind, dim=16, rot=8, heads=2, kv=1, far=40, rows=12):
     """The same for the grouped-query attentions, which see every earlier key: ``kind`` 'attention' (biases, a query
     factor, a score by distance) or 'attention_2' (rotation over the first ``rot`` dims, a sink)."""
     if kind == "attention":
-        mixer = biased(heads, kv, dim, q_temp=(0.3, 128), far=far, rows=rows, scale=1.0)
+        mixer = biased(heads, kv, dim, q_temp=(0.25, 96), far=far, rows=rows, scale=1.0)
     else:
         mixer = turned(heads, kv, dim, rot=rot, base=100.0, scaling=BANDS, scale=1.0)
     cfg = model(32, 64, [layer(kind, mixer)], mult=1.0, emb_scale=1.0, bigram=(11, 3, 2))

@@ -17,7 +17,7 @@ from spissa_b200.weights import write_random_model
 
 CFG = M.model(40, 90, [
     M.layer("latent_attention", M.through_rows(3, 8, 4, 12, 20, 9, base=100.0, scaling=M.RAMP), 56),
-    M.layer("attention", M.biased(4, 2, 6, vdim=10, q_temp=(0.3, 16), far=40, rows=12), 48),
+    M.layer("attention", M.biased(4, 2, 6, vdim=10, q_temp=(0.35, 16), far=40, rows=12), 48),
     M.layer("latent_attention", M.through_rows(2, 16, 4, 4, 20, 70, base=100.0, scaling=M.RAMP, kv_from=0)),
     M.layer("attention_2", M.turned(3, 3, 8, rot=4, base=50.0, scaling=M.BANDS), 24)],
     mult=0.5, emb_scale=8.0, bigram=(37, 5, 3), side=6, eps=1e-4)
