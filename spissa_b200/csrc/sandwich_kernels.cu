@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(128) gated_qkv_store_kernel(GatedQkvArgs a) {
     const int off = pos % a.pl.page_size;
     const float* src = a.proj + (size_t)t * a.ld;
     const float temp = a.temp_coef != 0.0f
-        ? 1.0f + a.temp_coef * logf(floorf((float)(pos + 1) / (float)a.temp_every) + 1.0f) : 1.0f;
+        ? 1.0f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.0f) : 1.0f;       // the quotient of integers: exact
     TO* q_out = (TO*)a.q_out;
     TC* kpool = (TC*)a.kpool;
     TC* vpool = (TC*)a.vpool;
