@@ -26,7 +26,7 @@ import math
 import torch
 
 from ..csrc import lib as K
-from .attention import attend_paged, length_bucket
+from .attention import attend_paged
 from .base import KVCacheRequest, Mixer, WeightSpec
 from .linear import Linear
 from .registry import build_part, register_part

@@ -195,13 +195,19 @@ class RotaryLatentAttention(Mixer):
         score_h(i, j) = ((U_k,h c_j) · q_i,h° + k_j^r · q_i,h^r) · scale    over i − w < j <= i (``window`` w; None: all)
         y += W_o · concat_h( sigmoid(w_g,h · x) · U_v,h Σ_j p_h(i, j) c_j )
 
-    Keys and values are never expanded. A page row is r_j = [c_j | k_j^r]; with the per-head map
+    What is cached is never the expanded keys and values. A page row is r_j = [c_j | k_j^r]; with the per-head map
     E_h = [[U_k,hᵀ, 0], [0, I]] the score is (E_h q_i,h) · r_j, so the query is carried into the rows' space once per
     token, the attention runs over the cached rows as they lie (one row is key and value, for all heads), and the
     weighted sum of rows is expanded once per token by [U_v,h | 0]. A layer built with ``shares_latent`` has no D and
     no norm weight: it reads the rows another layer cached (a run with ``cache.writes`` False), with its own q, U_k,
     U_v, gates and window. ``cache_window``: the window the cache keeps rows for when readers with other windows
-    share it."""
+    share it.
+
+    Three ways through it, chosen per step (bfloat16; the 32-bit mode takes the last): a step of 256 tokens or more in
+    which every sequence starts at its first token expands the step's own rows into keys [U_k,h c | k^r] and values
+    U_v,h c (two plain products over the rows) and runs on the tcgen05 prompt kernel, where that takes the sizes; other
+    steps of more than 64 tokens take both maps multiplied out into the products before and behind them; short steps
+    the small per-head products."""
     graph_safe = True
     kernel_modules = ("sandwich", "latent")
     kernel_modules_bf16 = ("attention",)
